@@ -1,0 +1,135 @@
+/*
+ * hsa_b200 — C ABI of the B200 (sm_100a) hierarchical sparse attention library.
+ *
+ * Every entry point replaces one host-side interface of the reference project's
+ * `hierarchical_attention` package (paths below are inside that project).  The
+ * library is stream-ordered and never synchronises; unless a function says
+ * otherwise it allocates nothing: outputs and scratch are the caller's.
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers, except where a parameter says "host".
+ *   - A tensor is passed as an hsa_view: base pointer plus batch and row strides
+ *     in ELEMENTS.  The innermost [H, D] block of a row is contiguous.
+ *   - dtype: 0 = float32, 1 = bfloat16, 2 = float16.  Accumulation is float32.
+ *   - Key/value rows are ordered [N leaves | level-1 parents | ... | root]
+ *     (2N-1 rows), as in hierarchical_attention/modules/attention.py:178.
+ *   - Return value: 0 = ok; < 0 = invalid argument (hsa_last_error() explains);
+ *     > 0 = a cudaError_t from the launch.
+ *   - `stream` is a cudaStream_t passed as void*.
+ */
+#ifndef HSA_B200_H
+#define HSA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HSA_F32 0
+#define HSA_BF16 1
+#define HSA_F16 2
+
+#define HSA_ERR_ARG (-1)      /* bad shape, size or flag              */
+#define HSA_ERR_ALIGN (-2)    /* pointer or stride breaks alignment   */
+#define HSA_ERR_DTYPE (-3)    /* unknown dtype code                   */
+#define HSA_ERR_WORKSPACE (-4)/* workspace missing or too small       */
+
+typedef struct hsa_view {
+    void *ptr;
+    int64_t batch_stride; /* elements between consecutive batch entries */
+    int64_t row_stride;   /* elements between consecutive node rows     */
+} hsa_view;
+
+/* Library version, major*10000 + minor*100 + patch. */
+int hsa_version(void);
+
+/* Message of the last error on the calling thread ("" if none).  Host string. */
+const char *hsa_last_error(void);
+
+/* Compute capability the kernels were compiled for (100 for sm_100a). */
+int hsa_compiled_arch(void);
+
+/*
+ * Tree topology tables.  Replaces build_tree_topology
+ * (hierarchical_attention/ops/topology.py:6-150).
+ *   fwd_idx  [N, L] int32 : key row of the sibling subtree leaf n sees at level l
+ *   fwd_mask [N, L] uint8 : 1 = excluded (future) when causal, else 0
+ *   gather   [2N-1, 3] int32 : (start, end, level) leaf range feeding each node's
+ *                              gradient, or (-1,-1,-1)
+ * N must be a power of two, N >= 1; L = log2 N.  Any output pointer may be NULL.
+ */
+int hsa_topology_build(int N, int causal, int32_t *fwd_idx, uint8_t *fwd_mask,
+                       int32_t *gather, void *stream);
+
+/*
+ * Initial parents: pairwise-mean pyramid.  Replaces generate_span_input_Y
+ * (hierarchical_attention/ops/topology.py:153-169).
+ *   x [B, N, d] -> y [B, M, d], M = hsa_span_input_y_rows(N); each level is
+ *   rounded to the storage dtype as the reference's per-level torch ops do.
+ * Any N >= 2 (odd tails are dropped level by level, as in the reference).
+ */
+int64_t hsa_span_input_y_rows(int64_t N);
+int hsa_span_input_y_fwd(hsa_view x, hsa_view y, int B, int N, int d, int dtype, void *stream);
+/* gx [B, N, d] = gradient of the pyramid w.r.t. x given gy [B, M, d]. */
+int hsa_span_input_y_bwd(hsa_view gy, hsa_view gx, int B, int N, int d, int dtype, void *stream);
+
+/*
+ * Parent-node update, one tree level.  Replaces build_parent_nodes /
+ * BuildParentNodesFunc.forward (hierarchical_attention/ops/functional.py:28-62,271)
+ * and its kernel (ops/triton/build_parents.py:8-99).
+ *   Qp, Kp, Vp, Out : [B, P, H, D];  Kc, Vc : [B, 2P, H, D]  (children of parent i
+ *   are rows 2i, 2i+1).  W, if not NULL, receives the three softmax weights
+ *   [B, P, H, 3] float32 contiguous.
+ */
+int hsa_parent_nodes_fwd(hsa_view Qp, hsa_view Kp, hsa_view Vp, hsa_view Kc, hsa_view Vc,
+                         hsa_view Out, float *W, int B, int P, int H, int D, int dtype,
+                         void *stream);
+
+/*
+ * Backward of the parent-node update.  Replaces BuildParentNodesFunc.backward
+ * (ops/functional.py:65-111; ops/triton/build_parents.py:106-204).  The softmax
+ * weights are recomputed from Q/K in float32; every gradient row has one writer.
+ */
+int hsa_parent_nodes_bwd(hsa_view dOut, hsa_view Qp, hsa_view Kp, hsa_view Vp, hsa_view Kc,
+                         hsa_view Vc, hsa_view dQp, hsa_view dKp, hsa_view dVp, hsa_view dKc,
+                         hsa_view dVc, int B, int P, int H, int D, int dtype, void *stream);
+
+/*
+ * Span attention forward.  Replaces hierarchical_attention /
+ * HierarchicalAttentionFunc.forward (ops/functional.py:114-168,274;
+ * ops/triton/sparse_attn.py:8-179).
+ *   Q, Out : [B, N, H, D];  K, V : [B, 2N-1, H, D].
+ *   Each leaf n attends to leaves n-R..n+R (causal: n-R..n) and to one sibling
+ *   node per level l (causal: only where bit l of n is set), joint softmax,
+ *   scale 1/sqrt(D).  `radius` is the reference's window_size.
+ *   LSE, if not NULL, receives log-sum-exp of the scaled logits [B, N, H] float32
+ *   (what the backward needs; the reference stores all weights instead).
+ *   The tree tables are generated in closed form inside the kernel; they equal
+ *   hsa_topology_build's output bit for bit.
+ *   `algo`: 0 = automatic, 1 = portable CUDA-core kernel, 2 = tensor-core kernel
+ *   (bf16/f16, D in {64,128} only; HSA_ERR_ARG otherwise).
+ */
+int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N,
+                      int H, int D, int radius, int causal, int dtype, int algo, void *stream);
+
+/*
+ * Span attention backward.  Replaces HierarchicalAttentionFunc.backward
+ * (ops/functional.py:170-264; ops/triton/sparse_attn.py:185-624).
+ *   Inputs Q, K, V, Out, LSE (from the forward) and dOut [B, N, H, D];
+ *   outputs dQ [B, N, H, D], dK, dV [B, 2N-1, H, D] — every row written, rows
+ *   nobody attends to get zeros.  Deterministic: no floating-point atomics.
+ *   `workspace` must hold hsa_span_attn_bwd_workspace_bytes(...) bytes, 256-byte aligned.
+ */
+size_t hsa_span_attn_bwd_workspace_bytes(int B, int N, int H, int D, int radius, int causal,
+                                         int dtype, int algo);
+int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const float *LSE,
+                      hsa_view dOut, hsa_view dQ, hsa_view dK, hsa_view dV, void *workspace,
+                      size_t workspace_bytes, int B, int N, int H, int D, int radius, int causal,
+                      int dtype, int algo, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HSA_B200_H */

@@ -21,6 +21,7 @@ Reference citations use paths inside the reference project.
 """
 from __future__ import annotations
 
+import functools
 import hashlib
 import math
 from typing import Dict, List, Optional, Tuple
@@ -151,6 +152,7 @@ def build_parent_nodes(Q_p, K_p, V_p, K_c, V_c, compute_dtype=torch.float32):
 # Op level: span attention (window + one sibling node per level)
 # ---------------------------------------------------------------------------
 
+@functools.lru_cache(maxsize=16)
 def span_candidates(N: int, radius: int, is_causal: bool):
     """(rows [N, 2R+1+L] int64, valid [N, 2R+1+L] bool): candidate key rows per leaf.
 
@@ -175,8 +177,11 @@ def span_candidates(N: int, radius: int, is_causal: bool):
 
 
 def hierarchical_attention(Q, K, V, radius: int, is_causal: bool, compute_dtype=torch.float32,
-                           return_lse: bool = False):
+                           return_lse: bool = False, leaves: Optional[torch.Tensor] = None):
     """Span attention on given Q [B,N,H,D], K,V [B,2N-1,H,D] (leaves then parents).
+
+    `leaves` (int64 indices) restricts the evaluation to those query rows (each leaf is
+    independent); the result then has len(leaves) rows.
 
     Joint softmax over the valid window slots and level slots
     (hierarchical_attention/ops/triton/sparse_attn.py:57-179; eager twin :277-339).
@@ -187,6 +192,8 @@ def hierarchical_attention(Q, K, V, radius: int, is_causal: bool, compute_dtype=
     assert K.shape[1] == 2 * N - 1
     rows, valid = span_candidates(N, radius, is_causal)
     q = Q.to(compute_dtype)
+    if leaves is not None:
+        rows, valid, q = rows[leaves], valid[leaves], q[:, leaves]
     k = K.to(compute_dtype)[:, rows]            # B,N,C,H,D
     v = V.to(compute_dtype)[:, rows]
     logits = torch.einsum("bnhd,bnchd->bnhc", q, k) / math.sqrt(D)

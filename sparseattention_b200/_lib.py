@@ -1,0 +1,117 @@
+"""ctypes binding of libhsa_b200.so (the C ABI declared in include/hsa_b200.h).
+
+There is no fallback: if the library is missing or a call fails, the caller gets an exception.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint8, c_void_p
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libhsa_b200.so")
+
+HSA_F32, HSA_BF16, HSA_F16 = 0, 1, 2
+_DTYPE_CODE = {torch.float32: HSA_F32, torch.bfloat16: HSA_BF16, torch.float16: HSA_F16}
+
+ALGO_AUTO, ALGO_PORTABLE, ALGO_TENSOR_CORE = 0, 1, 2
+
+
+class HsaView(Structure):
+    _fields_ = [("ptr", c_void_p), ("batch_stride", c_int64), ("row_stride", c_int64)]
+
+
+class HsaError(RuntimeError):
+    pass
+
+
+# name -> (restype, argtypes); one entry per declaration in include/hsa_b200.h
+V = HsaView
+SIGNATURES = {
+    "hsa_version": (c_int, []),
+    "hsa_last_error": (c_char_p, []),
+    "hsa_compiled_arch": (c_int, []),
+    "hsa_topology_build": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "hsa_span_input_y_rows": (c_int64, [c_int64]),
+    "hsa_span_input_y_fwd": (c_int, [V, V, c_int, c_int, c_int, c_int, c_void_p]),
+    "hsa_span_input_y_bwd": (c_int, [V, V, c_int, c_int, c_int, c_int, c_void_p]),
+    "hsa_parent_nodes_fwd": (c_int, [V, V, V, V, V, V, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "hsa_parent_nodes_bwd": (c_int, [V] * 11 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "hsa_span_attn_fwd": (c_int, [V, V, V, V, c_void_p] + [c_int] * 8 + [c_void_p]),
+    "hsa_span_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 8),
+    "hsa_span_attn_bwd": (c_int, [V, V, V, V, c_void_p, V, V, V, V, c_void_p, c_size_t] + [c_int] * 8 + [c_void_p]),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once).  Raises HsaError when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise HsaError(
+                f"{LIB_PATH} not found. Build it with `python -m sparseattention_b200.build` "
+                "(needs nvcc); this package has no CPU or PyTorch fallback.")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = lib
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load().hsa_last_error().decode(errors="replace")
+        raise HsaError(f"{what} failed (code {rc}): {msg}")
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise HsaError(f"unsupported dtype {t.dtype}; use float32, bfloat16 or float16") from None
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise HsaError("hsa_b200 ops take CUDA tensors only (there is no CPU path)")
+        if t.device != dev:
+            raise HsaError("all tensors of one call must live on the same device")
+    return dev
+
+
+def rows_view(t: torch.Tensor) -> HsaView:
+    """View of a [B, rows, ...] tensor whose trailing dims form one contiguous row."""
+    return HsaView(t.data_ptr(), t.stride(0), t.stride(1))
+
+
+def inner_contiguous(t: torch.Tensor) -> bool:
+    """True when dims 2.. of t are packed (so a row is one contiguous block)."""
+    expect = 1
+    for size, stride in zip(reversed(t.shape[2:]), reversed(t.stride()[2:])):
+        if size != 1 and stride != expect:
+            return False
+        expect *= size
+    return True
+
+
+def as_rows(t: torch.Tensor) -> torch.Tensor:
+    """Returns t itself when its rows are packed, else a contiguous copy."""
+    return t if inner_contiguous(t) else t.contiguous()
+
+
+def stream_ptr(dev: torch.device) -> c_void_p:
+    return c_void_p(torch.cuda.current_stream(dev).cuda_stream)

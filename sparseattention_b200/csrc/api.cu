@@ -1,0 +1,78 @@
+// C ABI glue: error reporting, version, and the algorithm choice for span attention.
+#include <cstdarg>
+#include <cstdio>
+
+#include "hsa_common.cuh"
+
+namespace hsa {
+namespace {
+thread_local char g_err[512] = "";
+}
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+}  // namespace hsa
+
+using namespace hsa;
+
+int hsa_span_attn_fwd_generic(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H,
+                              int D, int radius, int causal, int dtype, cudaStream_t st);
+size_t hsa_span_attn_bwd_generic_workspace(int B, int N, int H);
+int hsa_span_attn_bwd_generic(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const float *LSE, hsa_view dOut,
+                              hsa_view dQ, hsa_view dK, hsa_view dV, void *workspace, int B, int N, int H, int D,
+                              int radius, int causal, int dtype, cudaStream_t st);
+
+extern "C" int hsa_version(void) { return 100; }   // 0.1.0
+
+extern "C" const char *hsa_last_error(void) { return g_err; }
+
+extern "C" int hsa_compiled_arch(void) {
+#ifdef HSA_TARGET_ARCH
+    return HSA_TARGET_ARCH;
+#else
+    return 0;
+#endif
+}
+
+extern "C" int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N,
+                                 int H, int D, int radius, int causal, int dtype, int algo, void *stream) {
+    HSA_CHECK_ARG(Q.ptr && K.ptr && V.ptr && Out.ptr, "hsa_span_attn_fwd: null pointer");
+    HSA_CHECK_ARG(algo >= 0 && algo <= 2, "hsa_span_attn_fwd: unknown algo %d", algo);
+    HSA_CHECK_ARG(algo != 2, "hsa_span_attn_fwd: the tensor-core kernel is not built into this library");
+    return hsa_span_attn_fwd_generic(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, (cudaStream_t)stream);
+}
+
+extern "C" size_t hsa_span_attn_bwd_workspace_bytes(int B, int N, int H, int D, int radius, int causal,
+                                                    int dtype, int algo) {
+    (void)D; (void)radius; (void)causal; (void)dtype; (void)algo;
+    if (B < 1 || N < 1 || H < 1) return 0;
+    return hsa_span_attn_bwd_generic_workspace(B, N, H);
+}
+
+extern "C" int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const float *LSE,
+                                 hsa_view dOut, hsa_view dQ, hsa_view dK, hsa_view dV, void *workspace,
+                                 size_t workspace_bytes, int B, int N, int H, int D, int radius, int causal,
+                                 int dtype, int algo, void *stream) {
+    HSA_CHECK_ARG(Q.ptr && K.ptr && V.ptr && Out.ptr && LSE && dOut.ptr && dQ.ptr && dK.ptr && dV.ptr,
+                  "hsa_span_attn_bwd: null pointer");
+    HSA_CHECK_ARG(algo >= 0 && algo <= 2, "hsa_span_attn_bwd: unknown algo %d", algo);
+    HSA_CHECK_ARG(algo != 2, "hsa_span_attn_bwd: the tensor-core kernel is not built into this library");
+    const size_t need = hsa_span_attn_bwd_workspace_bytes(B, N, H, D, radius, causal, dtype, algo);
+    if (workspace == nullptr || workspace_bytes < need)
+        return fail(HSA_ERR_WORKSPACE, "hsa_span_attn_bwd: workspace of %zu bytes needed, %zu given", need,
+                    workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+        return fail(HSA_ERR_ALIGN, "hsa_span_attn_bwd: workspace must be 256-byte aligned");
+    return hsa_span_attn_bwd_generic(Q, K, V, Out, LSE, dOut, dQ, dK, dV, workspace, B, N, H, D, radius, causal,
+                                     dtype, (cudaStream_t)stream);
+}

@@ -1,0 +1,178 @@
+"""Functional ops of the hierarchical attention path, backed by the CUDA library.
+
+Mirrors hierarchical_attention/ops/functional.py of the reference project:
+`build_parent_nodes` (:271) and `hierarchical_attention` (:274), with the same argument
+meaning, output dtype (= input dtype) and autograd contract (tables and window_size get no
+gradient).  Differences a caller can observe:
+  * the backward is deterministic (no floating-point atomics);
+  * instead of the softmax weights the forward saves one log-sum-exp per (batch, leaf, head);
+  * batch-strided views (as produced by torch.split along dim 1) are consumed without a copy.
+"""
+from __future__ import annotations
+
+import math
+from ctypes import c_void_p
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+# ---------------------------------------------------------------------------------------------
+# build_parent_nodes
+# ---------------------------------------------------------------------------------------------
+
+
+class BuildParentNodesFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, Q_p, K_p, V_p, K_c, V_c):
+        lib = _lib.load()
+        dev = _lib.require_cuda(Q_p, K_p, V_p, K_c, V_c)
+        Q_p, K_p, V_p, K_c, V_c = (_lib.as_rows(t) for t in (Q_p, K_p, V_p, K_c, V_c))
+        B, P, H, D = Q_p.shape
+        assert K_c.shape[1] == 2 * P, "Child count mismatch"
+        assert K_p.shape == Q_p.shape == V_p.shape and V_c.shape == K_c.shape == (B, 2 * P, H, D)
+        dt = _lib.dtype_code(Q_p)
+        assert all(t.dtype == Q_p.dtype for t in (K_p, V_p, K_c, V_c)), "dtype mismatch"
+        Out = torch.empty((B, P, H, D), dtype=Q_p.dtype, device=dev)
+        with torch.cuda.device(dev):
+            rc = lib.hsa_parent_nodes_fwd(*(_lib.rows_view(t) for t in (Q_p, K_p, V_p, K_c, V_c, Out)),
+                                          None, B, P, H, D, dt, _lib.stream_ptr(dev))
+        _lib.check(rc, "hsa_parent_nodes_fwd")
+        ctx.save_for_backward(Q_p, K_p, V_p, K_c, V_c)
+        return Out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        lib = _lib.load()
+        Q_p, K_p, V_p, K_c, V_c = ctx.saved_tensors
+        dev = Q_p.device
+        B, P, H, D = Q_p.shape
+        grad_output = _lib.as_rows(grad_output)
+        dQ, dKp, dVp = (torch.empty((B, P, H, D), dtype=Q_p.dtype, device=dev) for _ in range(3))
+        dKc, dVc = (torch.empty((B, 2 * P, H, D), dtype=Q_p.dtype, device=dev) for _ in range(2))
+        with torch.cuda.device(dev):
+            rc = lib.hsa_parent_nodes_bwd(
+                *(_lib.rows_view(t) for t in (grad_output, Q_p, K_p, V_p, K_c, V_c, dQ, dKp, dVp, dKc, dVc)),
+                B, P, H, D, _lib.dtype_code(Q_p), _lib.stream_ptr(dev))
+        _lib.check(rc, "hsa_parent_nodes_bwd")
+        return dQ, dKp, dVp, dKc, dVc
+
+
+def build_parent_nodes(Q_p, K_p, V_p, K_c, V_c):
+    """Three-way attention of every parent over (itself, left child, right child).
+
+    Q_p, K_p, V_p: [B, P, H, D]; K_c, V_c: [B, 2P, H, D]; returns [B, P, H, D].
+    """
+    return BuildParentNodesFunc.apply(Q_p, K_p, V_p, K_c, V_c)
+
+
+# ---------------------------------------------------------------------------------------------
+# hierarchical_attention (span attention)
+# ---------------------------------------------------------------------------------------------
+
+# The kernels derive the tree in closed form.  Tables passed by the caller are accepted for API
+# compatibility and verified (once per tensor) to be the canonical ones; anything else is refused
+# rather than silently ignored.
+_verified_tables: Dict[Tuple[int, int, int, Tuple[int, ...]], bool] = {}
+
+
+def _verify_tables(idx_table, mask_table, N: int) -> None:
+    L = int(math.log2(N)) if N > 1 else 0
+    assert idx_table.shape[0] == N and idx_table.shape[1] == L, \
+        f"idx_table shape {tuple(idx_table.shape)} does not match N={N}, levels={L}"
+    if mask_table is not None:
+        assert tuple(mask_table.shape) == (N, L), "mask_table shape mismatch"
+    for t, kind in ((idx_table, 0), (mask_table, 1)):
+        if t is None or t.numel() == 0:
+            continue
+        key = (t.data_ptr(), t._version, kind, tuple(t.shape))
+        if key in _verified_tables:
+            continue
+        n = torch.arange(N, device=t.device).unsqueeze(1)
+        l = torch.arange(L, device=t.device).unsqueeze(0)
+        if kind == 0:
+            base = torch.where(l == 0, torch.zeros_like(l), 2 * N - (torch.full_like(l, N) >> (l - 1).clamp_min(0)))
+            want = base + ((n >> l) ^ 1)
+            ok = bool((t.to(torch.int64) == want).all())
+        else:
+            want = ((n >> l) & 1) == 0
+            ok = bool((t.to(torch.bool) == want).all())
+        if not ok:
+            raise _lib.HsaError(
+                "hierarchical_attention: the tables passed are not the canonical binary-tree topology "
+                "(build_tree_topology); custom topologies are not supported")
+        if len(_verified_tables) > 256:
+            _verified_tables.clear()
+        _verified_tables[key] = True
+
+
+def span_attention_forward(Q, K, V, window_size: int, is_causal: bool, need_lse: bool = True,
+                           algo: int = _lib.ALGO_AUTO):
+    """Raw forward on [B,N,H,D] / [B,2N-1,H,D] tensors: returns (Out, LSE or None). No autograd."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(Q, K, V)
+    Q, K, V = (_lib.as_rows(t) for t in (Q, K, V))
+    B, N, H, D = Q.shape
+    assert K.shape == (B, 2 * N - 1, H, D) and V.shape == K.shape, "K/V must be [B, 2N-1, H, D]"
+    assert K.dtype == Q.dtype and V.dtype == Q.dtype, "dtype mismatch"
+    Out = torch.empty((B, N, H, D), dtype=Q.dtype, device=dev)
+    LSE = torch.empty((B, N, H), dtype=torch.float32, device=dev) if need_lse else None
+    with torch.cuda.device(dev):
+        rc = lib.hsa_span_attn_fwd(*(_lib.rows_view(t) for t in (Q, K, V, Out)),
+                                   c_void_p(LSE.data_ptr()) if need_lse else None,
+                                   B, N, H, D, int(window_size), int(is_causal), _lib.dtype_code(Q), algo,
+                                   _lib.stream_ptr(dev))
+    _lib.check(rc, "hsa_span_attn_fwd")
+    return Out, LSE
+
+
+def span_attention_backward(Q, K, V, Out, LSE, dOut, window_size: int, is_causal: bool,
+                            algo: int = _lib.ALGO_AUTO):
+    """Raw backward: returns (dQ, dK, dV); dK/dV cover all 2N-1 rows."""
+    lib = _lib.load()
+    dev = Q.device
+    B, N, H, D = Q.shape
+    dOut = _lib.as_rows(dOut)
+    dQ = torch.empty((B, N, H, D), dtype=Q.dtype, device=dev)
+    dK = torch.empty((B, 2 * N - 1, H, D), dtype=Q.dtype, device=dev)
+    dV = torch.empty_like(dK)
+    dt = _lib.dtype_code(Q)
+    nbytes = int(lib.hsa_span_attn_bwd_workspace_bytes(B, N, H, D, int(window_size), int(is_causal), dt, algo))
+    ws = torch.empty((max(nbytes, 256) + 255) // 256 * 256, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.hsa_span_attn_bwd(
+            *(_lib.rows_view(t) for t in (Q, K, V, Out)), c_void_p(LSE.data_ptr()),
+            *(_lib.rows_view(t) for t in (dOut, dQ, dK, dV)), c_void_p(ws.data_ptr()), ws.numel(),
+            B, N, H, D, int(window_size), int(is_causal), dt, algo, _lib.stream_ptr(dev))
+    _lib.check(rc, "hsa_span_attn_bwd")
+    return dQ, dK, dV
+
+
+class HierarchicalAttentionFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, Q, K, V, idx_table, gather_table, mask_table=None, window_size=16):
+        B, N, H, D = Q.shape
+        _verify_tables(idx_table, mask_table, N)
+        is_causal = mask_table is not None
+        need_lse = any(ctx.needs_input_grad[:3])
+        Q, K, V = (_lib.as_rows(t) for t in (Q, K, V))
+        Out, LSE = span_attention_forward(Q, K, V, window_size, is_causal, need_lse=need_lse)
+        if need_lse:
+            ctx.save_for_backward(Q, K, V, Out, LSE)
+        ctx.window_size, ctx.is_causal = int(window_size), is_causal
+        return Out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        Q, K, V, Out, LSE = ctx.saved_tensors
+        dQ, dK, dV = span_attention_backward(Q, K, V, Out, LSE, grad_output, ctx.window_size, ctx.is_causal)
+        return dQ, dK, dV, None, None, None, None
+
+
+def hierarchical_attention(Q, K, V, idx_table, gather_table, mask_table=None, window_size=16):
+    """Span attention: each leaf attends to its radius-`window_size` window and to one sibling
+    node per tree level.  Q: [B,N,H,D]; K,V: [B,2N-1,H,D] (leaves then parents); returns [B,N,H,D].
+    `mask_table` not None selects the causal variant.
+    """
+    return HierarchicalAttentionFunc.apply(Q, K, V, idx_table, gather_table, mask_table, window_size)
