@@ -182,7 +182,7 @@ __device__ __forceinline__ void key_sources(int r, int N, int L, int R, int &w0,
     if (r < N) {
         w0 = CAUSAL ? r : max(0, r - R);
         w1 = min(N - 1, r + R) + 1;
-        if (!CAUSAL || (r & 1) == 0) { t0 = r ^ 1; t1 = t0 + 1; }
+        if (L > 0 && (!CAUSAL || (r & 1) == 0)) { t0 = r ^ 1; t1 = t0 + 1; }   // level-0 sibling
         return;
     }
     const int rem = 2 * N - r;

@@ -86,11 +86,11 @@ def test_span_input_y_golden_bit_exact(hsa, golden):
 def test_span_input_y_forward_backward(hsa, shape, dtype):
     gen = torch.Generator().manual_seed(3)
     x = torch.randn(*shape, generator=gen).to(dtype)
-    xo = x.clone().requires_grad_()
+    xo = x.detach().clone().requires_grad_()
     yo = orc.generate_span_input_Y(xo)
     gy = torch.randn(yo.shape, generator=gen).to(dtype)
     yo.backward(gy)
-    xc = x.cuda().requires_grad_()
+    xc = x.detach().cuda().requires_grad_()
     yc = hsa.generate_span_input_Y(xc)
     assert torch.equal(yc.detach().cpu(), yo.detach())           # bit-exact forward
     yc.backward(gy.cuda())
@@ -121,10 +121,10 @@ def test_parent_nodes_vs_oracle(hsa, B, P, H, D, dtype):
     shapes = [(B, P, H, D)] * 3 + [(B, 2 * P, H, D)] * 2
     ins = [torch.randn(*s, generator=gen).to(dtype) for s in shapes]
     go = torch.randn(B, P, H, D, generator=gen).to(dtype)
-    ref_in = [t.float().requires_grad_() for t in ins]
+    ref_in = [t.detach().float().clone().requires_grad_() for t in ins]
     ro = orc.build_parent_nodes(*ref_in)
     ro.backward(go.float())
-    cu_in = [t.cuda().requires_grad_() for t in ins]
+    cu_in = [t.detach().cuda().requires_grad_() for t in ins]
     co = hsa.build_parent_nodes(*cu_in)
     assert co.dtype == dtype and co.shape == (B, P, H, D)
     co.backward(go.cuda())
@@ -180,7 +180,7 @@ def run_span_case(hsa, B, N, H, D, R, causal, dtype, algo=0, seed=0, check_grad=
     K = torch.randn(B, 2 * N - 1, H, D, generator=gen).to(dtype)
     V = torch.randn(B, 2 * N - 1, H, D, generator=gen).to(dtype)
     go = torch.randn(B, N, H, D, generator=gen).to(dtype)
-    q, k, v = (t.float().requires_grad_() for t in (Q, K, V))
+    q, k, v = (t.detach().float().clone().requires_grad_() for t in (Q, K, V))
     ro, rlse = orc.hierarchical_attention(q, k, v, R, causal, return_lse=True)
     Qc, Kc, Vc = Q.cuda(), K.cuda(), V.cuda()
     out, lse = F.span_attention_forward(Qc, Kc, Vc, R, causal, need_lse=True, algo=algo)
@@ -196,7 +196,8 @@ def run_span_case(hsa, B, N, H, D, R, causal, dtype, algo=0, seed=0, check_grad=
     assert rel_err(dk.float().cpu(), k.grad) < tol
     assert rel_err(dv.float().cpu(), v.grad) < tol
     # rows nobody attends to (root; right children when causal) must be exact zeros
-    assert float(dk[:, 2 * N - 2].abs().max()) == 0.0 and float(dv[:, 2 * N - 2].abs().max()) == 0.0
+    if N > 1:
+        assert float(dk[:, 2 * N - 2].abs().max()) == 0.0 and float(dv[:, 2 * N - 2].abs().max()) == 0.0
     dq2, dk2, dv2 = F.span_attention_backward(Qc, Kc, Vc, out, lse, go.cuda(), R, causal, algo=algo)
     assert torch.equal(dk, dk2) and torch.equal(dv, dv2) and torch.equal(dq, dq2)   # deterministic
 
