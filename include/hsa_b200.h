@@ -129,6 +129,25 @@ int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const fl
                       size_t workspace_bytes, int B, int N, int H, int D, int radius, int causal,
                       int dtype, int algo, void *stream);
 
+/*
+ * Span attention backward without any workspace argument.  No counterpart in the reference
+ * project: it exists for hosts that cannot allocate device memory around the call (a plugin
+ * execute hook that only receives pre-bound buffers; a server whose GPU memory is fully
+ * partitioned at start-up).  Same inputs, outputs and results as hsa_span_attn_bwd with the
+ * portable kernels; the scratch is a fixed array inside the library image, so
+ *   - B*N*H must not exceed HSA_STATIC_SCRATCH_MAX_ELEMS (else HSA_ERR_WORKSPACE);
+ *   - every GPU that loads the library holds that array (4 MiB) until the process exits;
+ *   - all calls on one device share it: two calls that may run concurrently on the GPU
+ *     (different streams) race on it — serialise them;
+ *   - the first call on each device looks up the array's device address; make that first
+ *     call outside any stream capture, with the target device current.
+ * It calls no cudaMalloc/cudaFree and no allocating library routine.
+ */
+#define HSA_STATIC_SCRATCH_MAX_ELEMS (1 << 20)
+int hsa_span_attn_bwd_static(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const float *LSE,
+                             hsa_view dOut, hsa_view dQ, hsa_view dK, hsa_view dV, int B, int N,
+                             int H, int D, int radius, int causal, int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,7 +43,9 @@ SIGNATURES = {
     "hsa_span_attn_fwd": (c_int, [V, V, V, V, c_void_p] + [c_int] * 8 + [c_void_p]),
     "hsa_span_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 8),
     "hsa_span_attn_bwd": (c_int, [V, V, V, V, c_void_p, V, V, V, V, c_void_p, c_size_t] + [c_int] * 8 + [c_void_p]),
+    "hsa_span_attn_bwd_static": (c_int, [V, V, V, V, c_void_p, V, V, V, V] + [c_int] * 7 + [c_void_p]),
 }
+STATIC_SCRATCH_MAX_ELEMS = 1 << 20
 
 _lib = None
 _lock = threading.Lock()

@@ -376,3 +376,66 @@ int hsa_span_attn_bwd_generic(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, 
         return rc;
     });
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free backward.
+//
+// Some hosts of this library may not allocate device memory at the point where they call it: an
+// inference-engine plugin whose execute hook is handed pre-bound buffers only, or a serving loop
+// whose GPU memory was carved up at start-up and where a cudaMalloc would fail or stall every
+// stream of the process.  For them the per-(batch, leaf, head) scratch of the backward lives in the
+// library image itself, in the fixed array below, instead of a caller-supplied workspace.
+//
+// The array is a device symbol: in host code its name is only a handle, so the device address is
+// looked up once per device with cudaGetSymbolAddress (with that device current) and that address
+// is what the kernels receive.
+// ------------------------------------------------------------------------------------------------
+#include <mutex>
+
+namespace {
+static __device__ __align__(256) float g_static_scratch[HSA_STATIC_SCRATCH_MAX_ELEMS];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+float *g_static_addr[kMaxDevices] = {};
+
+// Device address of g_static_scratch on the current device (looked up on first use per device).
+int static_scratch_address(float **out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_bwd_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices)
+        return fail(HSA_ERR_ARG, "hsa_span_attn_bwd_static: device index %d beyond the %d supported", dev, kMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_addr[dev] == nullptr) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(e != cudaSuccess ? (int)e : HSA_ERR_WORKSPACE,
+                        "hsa_span_attn_bwd_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_static_addr[dev] = static_cast<float *>(p);
+    }
+    *out = g_static_addr[dev];
+    return 0;
+}
+}  // namespace
+
+extern "C" int hsa_span_attn_bwd_static(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const float *LSE,
+                                        hsa_view dOut, hsa_view dQ, hsa_view dK, hsa_view dV, int B, int N, int H,
+                                        int D, int radius, int causal, int dtype, void *stream) {
+    HSA_CHECK_ARG(Q.ptr && K.ptr && V.ptr && Out.ptr && LSE && dOut.ptr && dQ.ptr && dK.ptr && dV.ptr,
+                  "hsa_span_attn_bwd_static: null pointer");
+    if (int rc = check_span_shape("hsa_span_attn_bwd_static", B, N, H, D, radius)) return rc;
+    const long long elems = (long long)B * N * H;
+    if (elems > (long long)HSA_STATIC_SCRATCH_MAX_ELEMS)
+        return fail(HSA_ERR_WORKSPACE,
+                    "hsa_span_attn_bwd_static: B*N*H = %lld exceeds the built-in scratch of %lld entries; "
+                    "use hsa_span_attn_bwd with a caller workspace",
+                    elems, (long long)HSA_STATIC_SCRATCH_MAX_ELEMS);
+    float *scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    // Every scratch entry the key-side kernels read is written by the query-side kernel of the same
+    // call first, so nothing needs clearing between calls.
+    return hsa_span_attn_bwd_generic(Q, K, V, Out, LSE, dOut, dQ, dK, dV, scratch, B, N, H, D, radius, causal, dtype,
+                                     (cudaStream_t)stream);
+}
