@@ -32,6 +32,11 @@ int hsa_span_attn_bwd_generic(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, 
                               hsa_view dQ, hsa_view dK, hsa_view dV, void *workspace, int B, int N, int H, int D,
                               int radius, int causal, int dtype, cudaStream_t st);
 
+bool hsa_span_attn_fwd_tc_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, int B, int N, int H, int D,
+                                    int radius, int causal, int dtype);
+int hsa_span_attn_fwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H, int D,
+                         int radius, int causal, int dtype, cudaStream_t st);
+
 extern "C" int hsa_version(void) { return 100; }   // 0.1.0
 
 extern "C" const char *hsa_last_error(void) { return g_err; }
@@ -48,7 +53,8 @@ extern "C" int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Ou
                                  int H, int D, int radius, int causal, int dtype, int algo, void *stream) {
     HSA_CHECK_ARG(Q.ptr && K.ptr && V.ptr && Out.ptr, "hsa_span_attn_fwd: null pointer");
     HSA_CHECK_ARG(algo >= 0 && algo <= 2, "hsa_span_attn_fwd: unknown algo %d", algo);
-    HSA_CHECK_ARG(algo != 2, "hsa_span_attn_fwd: the tensor-core kernel is not built into this library");
+    if (algo == 2 || (algo == 0 && hsa_span_attn_fwd_tc_supported(Q, K, V, Out, B, N, H, D, radius, causal, dtype)))
+        return hsa_span_attn_fwd_tc(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, (cudaStream_t)stream);
     return hsa_span_attn_fwd_generic(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, (cudaStream_t)stream);
 }
 

@@ -191,6 +191,7 @@ def run_span_case(hsa, B, N, H, D, R, causal, dtype, algo=0, seed=0, check_grad=
     if not check_grad:
         return
     ro.backward(go.float())
+    algo = 0 if algo == 2 else algo
     dq, dk, dv = F.span_attention_backward(Qc, Kc, Vc, out, lse, go.cuda(), R, causal, algo=algo)
     assert rel_err(dq.float().cpu(), q.grad) < tol
     assert rel_err(dk.float().cpu(), k.grad) < tol
@@ -213,6 +214,33 @@ def test_span_attention_fp32_vs_oracle(hsa, case, causal):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_span_attention_half_vs_oracle_portable(hsa, case, causal, dtype):
     run_span_case(hsa, *case, causal, dtype, algo=1)
+
+
+TC_CASES = [(1, 64, 1, 64, 0), (2, 64, 3, 64, 5), (1, 128, 2, 128, 16), (2, 256, 3, 64, 8), (1, 512, 2, 128, 33),
+            (1, 1024, 1, 64, 16), (1, 4096, 2, 128, 16), (1, 2048, 1, 128, 60), (1, 256, 2, 64, 300),
+            (1, 16384, 1, 64, 16), (1, 65536, 1, 64, 1)]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_span_attention_tensor_core_forward(hsa, case, causal, dtype):
+    """The tensor-core forward (algo 2) against the oracle; backward through the default path."""
+    run_span_case(hsa, *case, causal, dtype, algo=2, check_grad=False)
+
+
+def test_tensor_core_kernel_refuses_what_it_cannot_take(hsa):
+    from sparseattention_b200._lib import HsaError
+    from sparseattention_b200.ops import functional as F
+    q = torch.randn(1, 32, 1, 64, device="cuda", dtype=torch.bfloat16)          # N < 64
+    kv = torch.randn(1, 63, 1, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(HsaError):
+        F.span_attention_forward(q, kv, kv, 4, True, algo=2)
+    q = torch.randn(1, 64, 1, 64, device="cuda")                                 # float32
+    kv = torch.randn(1, 127, 1, 64, device="cuda")
+    with pytest.raises(HsaError):
+        F.span_attention_forward(q, kv, kv, 4, True, algo=2)
+    F.span_attention_forward(q, kv, kv, 4, True, algo=0)                          # automatic choice still works
 
 
 def test_span_attention_rejects_foreign_tables(hsa):
