@@ -131,15 +131,23 @@ __device__ __forceinline__ BlockRef block_ref(int o, int RB, int nbb) {
     return {true, o};
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t ldg32(const void *p) { return __ldg(reinterpret_cast<const unsigned int *>(p)); }
+
 template <typename T, int D, bool CAUSAL>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 span_fwd_tc_kernel(SpanTcArgs a) {
     constexpr int PITCH = D * 2 + 16;          // bytes; the 16-byte skew keeps ldmatrix conflict-free
     constexpr int CPR = D / 8;                 // 16-byte chunks per row
+    constexpr int RPI = 128 / CPR;             // rows staged per pass of the CTA
     constexpr int KS = D / 16;                 // k-steps of the QK^T product
+    constexpr int TIN = tree_in_rows<CAUSAL>();
     extern __shared__ __align__(16) unsigned char smem[];
-    unsigned char *Qs = smem;
-    unsigned char *Ks = Qs + kTile * PITCH;
+    unsigned char *Ks = smem;
     unsigned char *Vs = Ks + (size_t)a.kv_rows * PITCH;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -147,104 +155,109 @@ span_fwd_tc_kernel(SpanTcArgs a) {
     const int tile = blockIdx.x / a.H;
     const int b = blockIdx.y;
     const int t0 = tile * kTile;
-    const int N = a.N, L = a.L;
-    const int band_lo = t0 - 16 * a.RB;
+    const int N = a.N, L = a.L, R = a.R, RB = a.RB;
+    const int band_lo = t0 - 16 * RB;
     const int64_t hoff = (int64_t)h * D;
     const T *qg = (const T *)a.q + b * a.q_bs + hoff;
     const T *kg = (const T *)a.k + b * a.k_bs + hoff;
     const T *vg = (const T *)a.v + b * a.v_bs + hoff;
 
-    // ---------------------------------------------------------------- stage Q, K (group 0) and V (group 1)
-    for (int idx = tid; idx < kTile * CPR; idx += 128) {
-        const int i = idx / CPR, c = idx % CPR;
-        cp_async16(smem_u32(Qs + i * PITCH + c * 16), qg + (int64_t)(t0 + i) * a.q_rs + c * 8, true);
-    }
-    auto stage_kv = [&](const T *g, int64_t rs, unsigned char *S) {
-        for (int idx = tid; idx < a.band_rows * CPR; idx += 128) {
-            const int i = idx / CPR, c = idx % CPR;
-            const int r = band_lo + i;
-            const bool ok = r >= 0 && r < N;
-            cp_async16(smem_u32(S + i * PITCH + c * 16), g + (int64_t)(ok ? r : 0) * rs + c * 8, ok);
-        }
-        constexpr int TIN = tree_in_rows<CAUSAL>();
-        for (int idx = tid; idx < TIN * CPR; idx += 128) {
-            const int f = idx / CPR, c = idx % CPR;
-            const int rem = (CAUSAL ? 32 : 64) - f;
-            const int l = (CAUSAL ? 5 : 6) - (31 - __clz(rem - 1));
-            const int i = f - tree_level_off<CAUSAL>(l);
-            const int jj = CAUSAL ? 2 * i : i;
-            const int r = level_base(N, l) + (t0 >> l) + jj;
-            cp_async16(smem_u32(S + (a.band_rows + f) * PITCH + c * 16), g + (int64_t)r * rs + c * 8, true);
-        }
-        const int nup = L - kTileLog;
-        for (int idx = tid; idx < nup * CPR; idx += 128) {
-            const int u = idx / CPR, c = idx % CPR;
-            const int l = kTileLog + u;
-            const bool ok = !CAUSAL || ((t0 >> l) & 1);
-            const int r = level_base(N, l) + ((t0 >> l) ^ 1);
-            cp_async16(smem_u32(S + (a.band_rows + TIN + u) * PITCH + c * 16), g + (int64_t)r * rs + c * 8, ok);
-        }
-    };
-    stage_kv(kg, a.k_rs, Ks);
-    cp_async_commit();
-    stage_kv(vg, a.v_rs, Vs);
-    cp_async_commit();
-
-    cp_async_wait<1>();
-    __syncthreads();
-
-    // ---------------------------------------------------------------- per-warp compute
     const int lw = 16 * warp;
     const int quad = lane & 3, qrow = lane >> 2;
     const int n0 = t0 + lw + qrow, n1 = n0 + 8;       // the two leaves this thread holds scores for
+
+    // ---------------------------------------------------------------- Q: global -> A-operand registers
     uint32_t qf[KS][4];
     {
-        const int row = lw + (lane & 7) + 8 * ((lane >> 3) & 1);
-        const int doff = 8 * (lane >> 4);
-        const uint32_t base = smem_u32(Qs + row * PITCH + doff * 2);
+        const T *q0 = qg + (int64_t)n0 * a.q_rs + 2 * quad;
+        const T *q1 = qg + (int64_t)n1 * a.q_rs + 2 * quad;
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) ldmatrix_x4(qf[ks], base + ks * 32);
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = ldg32(q0 + ks * 16);
+            qf[ks][1] = ldg32(q1 + ks * 16);
+            qf[ks][2] = ldg32(q0 + ks * 16 + 8);
+            qf[ks][3] = ldg32(q1 + ks * 16 + 8);
+        }
     }
+
+    // ---------------------------------------------------------------- stage K (group 0) and V (group 1)
+    {
+        const int c = tid % CPR, rg = tid / CPR;
+        const int ntree = TIN + (L - kTileLog);
+        auto stage_kv = [&](const T *g, int64_t rs, unsigned char *S) {
+            const T *gc = g + c * 8;
+            uint32_t dst = smem_u32(S) + rg * PITCH + c * 16;
+            int r = band_lo + rg;
+            for (int i = rg; i < a.band_rows; i += RPI, r += RPI, dst += RPI * PITCH) {
+                const bool ok = (unsigned)r < (unsigned)N;
+                cp_async16(dst, gc + (int64_t)(ok ? r : 0) * rs, ok);
+            }
+            dst = smem_u32(S) + (a.band_rows + rg) * PITCH + c * 16;
+            for (int f = rg; f < ntree; f += RPI, dst += RPI * PITCH) {
+                int rr;
+                bool ok = true;
+                if (f < TIN) {
+                    const int rem = (CAUSAL ? 32 : 64) - f;
+                    const int l = (CAUSAL ? 5 : 6) - (31 - __clz(rem - 1));
+                    const int i = f - tree_level_off<CAUSAL>(l);
+                    rr = level_base(N, l) + (t0 >> l) + (CAUSAL ? 2 * i : i);
+                } else {
+                    const int l = kTileLog + (f - TIN);
+                    ok = !CAUSAL || ((t0 >> l) & 1);
+                    rr = level_base(N, l) + ((t0 >> l) ^ 1);
+                }
+                cp_async16(dst, gc + (int64_t)rr * rs, ok);
+            }
+        };
+        stage_kv(kg, a.k_rs, Ks);
+        cp_async_commit();
+        stage_kv(vg, a.v_rs, Vs);
+        cp_async_commit();
+    }
+
+    const int nbb = CAUSAL ? RB + 1 : 2 * RB + 1;
+    const int ntb = (tree_slots<CAUSAL>(L) + 15) >> 4;
+    const int nblk = nbb + ntb;
+
+    // ---------------------------------------------------------------- masks (closed-form topology)
+    // Tree blocks: one validity bit per score element this thread will hold, bit = tb*8 + nt*4 + e.
+    uint32_t tree_bits = 0;
+    for (int tb = 0; tb < ntb; ++tb) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int slot = 16 * tb + nt * 8 + 2 * quad + (e & 1);
+                const int i = qrow + 8 * (e >> 1);
+                int row, jj;
+                const int l = tree_slot<CAUSAL>(slot, warp, L, row, jj);
+                bool ok = false;
+                if (l >= 1 && l <= 3) ok = CAUSAL ? ((i >> l) == jj + 1) : (((i >> l) ^ 1) == jj);
+                else if (l >= 4) ok = !CAUSAL || (((t0 + lw) >> l) & 1);
+                tree_bits |= (ok ? 1u : 0u) << ((tb & 3) * 8 + nt * 4 + e);
+            }
+    }
+    // Band blocks: key - leaf distance of element (nt, e) in band block bi is dbase + 16*(bi-RB) + nt*8 + (e&1) - 8*(e>>1)
+    const int dbase = 2 * quad - qrow;
+    const int sib_dlt = (qrow & 1) ? -1 : 1;                     // where the level-0 sibling sits
+    const bool sib_ok = !CAUSAL || (qrow & 1);
+
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    const int nbb = CAUSAL ? a.RB + 1 : 2 * a.RB + 1;
-    const int ntb = (tree_slots<CAUSAL>(L) + 15) >> 4;
-    const int nblk = nbb + ntb;
-    const int R = a.R;
-    const unsigned char *Kt = Ks + (size_t)a.band_rows * PITCH;     // tree rows of K
-    const unsigned char *Vt = Vs + (size_t)a.band_rows * PITCH;
-
     // shared-memory row of key `kk` (0..15) of ordered block o, relative to Ks / Vs
     auto key_row = [&](int o_idx, int kk) -> int {
-        const BlockRef br = block_ref<CAUSAL>(o_idx, a.RB, nbb);
+        const BlockRef br = block_ref<CAUSAL>(o_idx, RB, nbb);
         if (br.band) return lw + 16 * br.idx + kk;
         int row, jj;
         tree_slot<CAUSAL>(16 * br.idx + kk, warp, L, row, jj);
         return a.band_rows + row;
     };
-    // additive base-2 bias of (leaf n, local row i in the warp, key column col of ordered block o):
-    // -inf = not attended, 0 = attended once, 1 = attended twice (window slot and level-0 slot)
-    auto bias = [&](int o_idx, int col, int n, int i) -> float {
-        const BlockRef br = block_ref<CAUSAL>(o_idx, a.RB, nbb);
-        if (br.band) {
-            const int r = t0 + lw - 16 * a.RB + 16 * br.idx + col;
-            if (r < 0 || r >= N) return -INFINITY;
-            const int dlt = r - n;
-            const bool wv = (CAUSAL ? (dlt <= 0) : (dlt <= R)) && dlt >= -R;
-            const bool lv = (r == (n ^ 1)) && (!CAUSAL || (n & 1));
-            return (wv && lv) ? 1.f : ((wv || lv) ? 0.f : -INFINITY);
-        }
-        int row, jj;
-        const int l = tree_slot<CAUSAL>(16 * br.idx + col, warp, L, row, jj);
-        if (l < 0) return -INFINITY;
-        bool ok;
-        if (l <= 3) ok = CAUSAL ? ((i >> l) == jj + 1) : (((i >> l) ^ 1) == jj);
-        else ok = !CAUSAL || ((n >> l) & 1);
-        return ok ? 0.f : -INFINITY;
-    };
+
+    cp_async_wait<1>();
+    __syncthreads();
 
     const float c2 = a.scale_log2e;
     for (int c0 = 0; c0 < nblk; c0 += kChunk) {
@@ -264,14 +277,31 @@ span_fwd_tc_kernel(SpanTcArgs a) {
                     mma16816<T>(s[bi][0], qf[ks], kf[0], kf[1]);
                     mma16816<T>(s[bi][1], qf[ks], kf[2], kf[3]);
                 }
+                const BlockRef br = block_ref<CAUSAL>(c0 + bi, RB, nbb);
+                if (br.band) {
+                    const int r0 = t0 + lw + 16 * (br.idx - RB);          // first key row of the block
+                    const bool edge = r0 < 0 || r0 + 16 > N;
+                    const bool self = br.idx == RB;
+                    const int d0 = dbase + 16 * (br.idx - RB);
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
+                    for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int col = nt * 8 + 2 * quad + (e & 1);
-                        const int i = qrow + 8 * (e >> 1);
-                        s[bi][nt][e] = fmaf(s[bi][nt][e], c2, bias(c0 + bi, col, (e >> 1) ? n1 : n0, i));
-                    }
+                        for (int e = 0; e < 4; ++e) {
+                            const int dlt = d0 + nt * 8 + (e & 1) - 8 * (e >> 1);
+                            bool wv = dlt >= -R && dlt <= (CAUSAL ? 0 : R);
+                            if (edge) wv = wv && (unsigned)(r0 + nt * 8 + 2 * quad + (e & 1)) < (unsigned)N;
+                            const bool lv = self && sib_ok && dlt == sib_dlt;
+                            const float bias = (wv && lv) ? 1.f : ((wv || lv) ? 0.f : -INFINITY);
+                            s[bi][nt][e] = fmaf(s[bi][nt][e], c2, bias);
+                        }
+                } else {
+                    const uint32_t bits = tree_bits >> ((br.idx & 3) * 8);
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            s[bi][nt][e] = ((bits >> (nt * 4 + e)) & 1u) ? s[bi][nt][e] * c2 : -INFINITY;
+                }
             } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[bi][0][e] = s[bi][1][e] = -INFINITY;
@@ -292,7 +322,7 @@ span_fwd_tc_kernel(SpanTcArgs a) {
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite: chunk 0 holds the leaf itself
         if (c0 > 0) {
-            const float r0 = exp2f(m0 - mn0), r1 = exp2f(m1 - mn1);
+            const float r0 = fast_exp2(m0 - mn0), r1 = fast_exp2(m1 - mn1);
             l0 *= r0;
             l1 *= r1;
 #pragma unroll
@@ -309,10 +339,10 @@ span_fwd_tc_kernel(SpanTcArgs a) {
                 float p[2][4];
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
-                    p[nt][0] = exp2f(s[bi][nt][0] - m0);
-                    p[nt][1] = exp2f(s[bi][nt][1] - m0);
-                    p[nt][2] = exp2f(s[bi][nt][2] - m1);
-                    p[nt][3] = exp2f(s[bi][nt][3] - m1);
+                    p[nt][0] = fast_exp2(s[bi][nt][0] - m0);
+                    p[nt][1] = fast_exp2(s[bi][nt][1] - m0);
+                    p[nt][2] = fast_exp2(s[bi][nt][2] - m1);
+                    p[nt][3] = fast_exp2(s[bi][nt][3] - m1);
                     l0 += p[nt][0] + p[nt][1];
                     l1 += p[nt][2] + p[nt][3];
                 }
@@ -332,7 +362,6 @@ span_fwd_tc_kernel(SpanTcArgs a) {
             }
         }
     }
-    (void)Kt; (void)Vt;
 
     // ---------------------------------------------------------------- epilogue
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -345,9 +374,10 @@ span_fwd_tc_kernel(SpanTcArgs a) {
         a.lse[((int64_t)b * N + n0) * a.H + h] = (m0 + log2f(l0)) * kLn2;
         a.lse[((int64_t)b * N + n1) * a.H + h] = (m1 + log2f(l1)) * kLn2;
     }
-    // stage the warp's 16 output rows in its own (now unused) Q rows, then store 16 bytes per lane
-    __syncwarp();
-    unsigned char *Os = Qs + lw * PITCH;
+    // When every warp is done with K, each warp parks its 16 output rows in K's first rows and then
+    // stores them 16 bytes per lane (full 32-byte sectors, whole rows per request).
+    __syncthreads();
+    unsigned char *Os = Ks + lw * PITCH;
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
         const int col = nt * 8 + 2 * quad;
@@ -368,7 +398,7 @@ span_fwd_tc_kernel(SpanTcArgs a) {
 template <typename T, int D>
 static int launch_tc(const SpanTcArgs &a, int B, bool causal, cudaStream_t st) {
     constexpr int PITCH = D * 2 + 16;
-    const size_t smem = (size_t)(kTile + 2 * a.kv_rows) * PITCH;
+    const size_t smem = (size_t)(2 * a.kv_rows) * PITCH;
     dim3 grid((unsigned)((a.N / kTile) * a.H), (unsigned)B);
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -397,7 +427,7 @@ bool hsa_span_attn_fwd_tc_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_view
     const int L = ilog2((unsigned)N);
     const int band = kTile + 16 * RB * (causal ? 1 : 2);
     const int kv = band + (causal ? 31 : 62) + (L - kTileLog);
-    const size_t smem = (size_t)(kTile + 2 * kv) * (D * 2 + 16);
+    const size_t smem = (size_t)(2 * kv) * (D * 2 + 16);
     return smem <= 200 * 1024;
 }
 
