@@ -37,6 +37,13 @@ bool hsa_span_attn_fwd_tc_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_view
 int hsa_span_attn_fwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H, int D,
                          int radius, int causal, int dtype, cudaStream_t st);
 
+bool hsa_span_attn_bwd_tc_supported(const hsa_view *views, int nviews, int B, int N, int H, int D, int radius,
+                                    int causal, int dtype);
+size_t hsa_span_attn_bwd_tc_workspace(int B, int N, int H, int D);
+int hsa_span_attn_bwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const float *LSE, hsa_view dOut, hsa_view dQ,
+                         hsa_view dK, hsa_view dV, void *workspace, int B, int N, int H, int D, int radius, int causal,
+                         int dtype, cudaStream_t st);
+
 extern "C" int hsa_version(void) { return 100; }   // 0.1.0
 
 extern "C" const char *hsa_last_error(void) { return g_err; }
@@ -60,9 +67,15 @@ extern "C" int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Ou
 
 extern "C" size_t hsa_span_attn_bwd_workspace_bytes(int B, int N, int H, int D, int radius, int causal,
                                                     int dtype, int algo) {
-    (void)D; (void)radius; (void)causal; (void)dtype; (void)algo;
-    if (B < 1 || N < 1 || H < 1) return 0;
-    return hsa_span_attn_bwd_generic_workspace(B, N, H);
+    (void)radius; (void)causal;
+    if (B < 1 || N < 1 || H < 1 || D < 1) return 0;
+    // algo 0 may pick either kernel from the pointers it is given: size for the larger need
+    const size_t portable = hsa_span_attn_bwd_generic_workspace(B, N, H);
+    const bool tc_dtype = (dtype == HSA_BF16 || dtype == HSA_F16) && (D == 64 || D == 128) && N >= 64;
+    const size_t tc = tc_dtype ? hsa_span_attn_bwd_tc_workspace(B, N, H, D) : 0;
+    if (algo == 1) return portable;
+    if (algo == 2) return tc;
+    return portable > tc ? portable : tc;
 }
 
 extern "C" int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const float *LSE,
@@ -72,13 +85,16 @@ extern "C" int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Ou
     HSA_CHECK_ARG(Q.ptr && K.ptr && V.ptr && Out.ptr && LSE && dOut.ptr && dQ.ptr && dK.ptr && dV.ptr,
                   "hsa_span_attn_bwd: null pointer");
     HSA_CHECK_ARG(algo >= 0 && algo <= 2, "hsa_span_attn_bwd: unknown algo %d", algo);
-    HSA_CHECK_ARG(algo != 2, "hsa_span_attn_bwd: the tensor-core kernel is not built into this library");
     const size_t need = hsa_span_attn_bwd_workspace_bytes(B, N, H, D, radius, causal, dtype, algo);
     if (workspace == nullptr || workspace_bytes < need)
         return fail(HSA_ERR_WORKSPACE, "hsa_span_attn_bwd: workspace of %zu bytes needed, %zu given", need,
                     workspace_bytes);
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
         return fail(HSA_ERR_ALIGN, "hsa_span_attn_bwd: workspace must be 256-byte aligned");
+    const hsa_view views[] = {Q, K, V, Out, dOut, dQ, dK, dV};
+    if (algo == 2 || (algo == 0 && hsa_span_attn_bwd_tc_supported(views, 8, B, N, H, D, radius, causal, dtype)))
+        return hsa_span_attn_bwd_tc(Q, K, V, Out, LSE, dOut, dQ, dK, dV, workspace, B, N, H, D, radius, causal, dtype,
+                                    (cudaStream_t)stream);
     return hsa_span_attn_bwd_generic(Q, K, V, Out, LSE, dOut, dQ, dK, dV, workspace, B, N, H, D, radius, causal,
                                      dtype, (cudaStream_t)stream);
 }

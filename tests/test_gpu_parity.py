@@ -191,8 +191,13 @@ def run_span_case(hsa, B, N, H, D, R, causal, dtype, algo=0, seed=0, check_grad=
     if not check_grad:
         return
     ro.backward(go.float())
-    algo = 0 if algo == 2 else algo
-    dq, dk, dv = F.span_attention_backward(Qc, Kc, Vc, out, lse, go.cuda(), R, causal, algo=algo)
+    try:
+        dq, dk, dv = F.span_attention_backward(Qc, Kc, Vc, out, lse, go.cuda(), R, causal, algo=algo)
+    except Exception as exc:   # a window too wide for the backward's shared memory: the automatic choice takes over
+        if algo != 2 or "fits shared memory" not in str(exc):
+            raise
+        algo = 0
+        dq, dk, dv = F.span_attention_backward(Qc, Kc, Vc, out, lse, go.cuda(), R, causal, algo=algo)
     assert rel_err(dq.float().cpu(), q.grad) < tol
     assert rel_err(dk.float().cpu(), k.grad) < tol
     assert rel_err(dv.float().cpu(), v.grad) < tol
@@ -224,9 +229,9 @@ TC_CASES = [(1, 64, 1, 64, 0), (2, 64, 3, 64, 5), (1, 128, 2, 128, 16), (2, 256,
 @pytest.mark.parametrize("case", TC_CASES)
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_span_attention_tensor_core_forward(hsa, case, causal, dtype):
-    """The tensor-core forward (algo 2) against the oracle; backward through the default path."""
-    run_span_case(hsa, *case, causal, dtype, algo=2, check_grad=False)
+def test_span_attention_tensor_core(hsa, case, causal, dtype):
+    """The tensor-core forward and backward (algo 2) against the oracle."""
+    run_span_case(hsa, *case, causal, dtype, algo=2)
 
 
 def test_tensor_core_kernel_refuses_what_it_cannot_take(hsa):
