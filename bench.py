@@ -217,6 +217,58 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+LM_CONFIGS = {
+    # BASELINE configs 3 and 4: 6 layers, d_model 512, 8 heads, FFN 2048, window 16, vocab 50257, bf16
+    "lm_8x2048": dict(batch=8, seq=2048), "lm_8x4096": dict(batch=8, seq=4096),
+}
+
+
+def run_lm(args, device, world, rank, barrier, use_dist):
+    """Training step (forward, loss, backward, gradient all-reduce, clip, AdamW) of the hierarchical LM
+    on Zipf(1.1) token ids; per-GPU batch fixed (weak scaling).  Returns whole-job tokens/s."""
+    import torch.distributed as dist
+    from sparseattention_b200.dp import BucketedGradAverager
+    from sparseattention_b200.lm import TransformerLM, lm_loss, zipf_tokens
+
+    cfg = LM_CONFIGS[args.lm]
+    vocab = 50257
+    torch.manual_seed(0)
+    model = TransformerLM(vocab, 512, 8, 2048, 6, dropout=0.1, window_size=16).to(device)
+    avg = BucketedGradAverager(model.parameters())
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
+    host_tokens = zipf_tokens(cfg["batch"], cfg["seq"] + 1, vocab, seed=4321 + rank).pin_memory()
+    losses = []
+
+    def step():
+        tokens = host_tokens.to(device, non_blocking=True)
+        avg.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = lm_loss(model, tokens)
+        loss.backward()
+        avg.finish()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        losses.append(loss.detach())
+
+    steps = max(3, min(args.steps, 10))
+    ms = time_cuda(step, steps, 3, barrier)
+    if use_dist:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms /= steps
+    tok = cfg["batch"] * cfg["seq"] * world
+    nparams = sum(p.numel() for p in model.parameters())
+    out = {"config": args.lm, "tokens_per_s": tok / (ms * 1e-3), "ms_per_step": ms, "steps": steps,
+           "global_batch": cfg["batch"] * world, "seq_len": cfg["seq"], "params": nparams,
+           "allreduce_bytes_per_step": avg.bytes_per_step() if world > 1 else 0,
+           "loss_first": float(losses[0]), "loss_last": float(losses[-1]),
+           "step": "fwd + label-smoothed CE + bwd + NCCL grad all-reduce + clip + AdamW, bf16 autocast"}
+    del model, opt, avg
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     import sparseattention_b200 as hsa
     from sparseattention_b200 import _lib
@@ -323,6 +375,10 @@ def run_ours(args):
             "frac_of_hbm": palg / (pms * 1e-3) / 1e9 / peak}
         del Pq, Pk, Pv, Ck, Cv
 
+    # ---- the model that calls the layer: data-parallel LM training step (all ranks) ---------------
+    if not args.no_lm:
+        extras["lm_train"] = run_lm(args, device, world, rank, barrier, use_dist)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
@@ -368,6 +424,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-lm", action="store_true")
+    ap.add_argument("--lm", default="lm_8x4096", choices=sorted(LM_CONFIGS))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -434,3 +434,30 @@ def test_module_api_surface(hsa):
     x2 = torch.randn(1, 64, 64, device="cuda")
     y2 = m.cross_update_Y(x2, hsa.generate_span_input_Y(x2))
     assert y2.shape == (1, 63, 64) and m(x2, x2, x2, y=y2, mask=None).shape == (1, 64, 64)
+
+
+def test_language_model_against_oracle_layers(hsa):
+    """The LM that calls the layer (6 -> 2 layers, small widths), fp32: logits, loss and a few gradients
+    against the same model built around the CPU oracle layer."""
+    from sparseattention_b200.lm import TransformerLM, lm_loss, zipf_tokens
+    torch.backends.cuda.matmul.allow_tf32 = False
+    vocab, d, heads, ff, layers, N = 211, 64, 4, 128, 2, 64
+    torch.manual_seed(5)
+    ref = TransformerLM(vocab, d, heads, ff, layers, dropout=0.0, window_size=4,
+                        attention_cls=orc.HierarchicalAttentionOracle, span_init=orc.generate_span_input_Y).eval()
+    torch.manual_seed(5)
+    ours = TransformerLM(vocab, d, heads, ff, layers, dropout=0.0, window_size=4).eval()
+    ours.load_state_dict(ref.state_dict())
+    ours = ours.cuda()
+    tokens = zipf_tokens(2, N + 1, vocab, seed=9)
+    lr = lm_loss(ref, tokens)
+    lr.backward()
+    lo = lm_loss(ours, tokens.cuda())
+    lo.backward()
+    assert abs(float(lo) - float(lr)) < 1e-5 * abs(float(lr))
+    assert rel_err(ours(tokens[:, :-1].cuda()).detach().cpu(), ref(tokens[:, :-1]).detach()) < 1e-5
+    for name in ("embedding.weight", "layers.0.self_attn.Wk_y.weight", "layers.1.self_attn.Wq_x.weight",
+                 "layers.0.norm_y.weight", "layers.1.feed_forward.fc1.weight"):
+        g_ours = dict(ours.named_parameters())[name].grad.cpu()
+        g_ref = dict(ref.named_parameters())[name].grad
+        assert rel_err(g_ours, g_ref) < 2e-5, name
