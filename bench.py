@@ -282,6 +282,8 @@ def run_ours(args):
     use_dist = world > 1
     if use_dist:
         import torch.distributed as dist
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"          # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=device)
 
         def barrier():

@@ -10,7 +10,12 @@ measured inside the training step the reference measures.  Differences from the 
   * the causal "mask" handed to the layers is a 1-element tensor: the layer only tests it for
     `is not None` (the reference builds an N x N boolean matrix per forward for that purpose);
   * the attention class and the span initialiser are constructor arguments, so tests can run the
-    same model around the CPU oracle.
+    same model around the CPU oracle;
+  * the tied embedding / output matrix is stored with its vocabulary dimension padded up to a multiple
+    of 64 rows (50257 -> 50304).  The extra rows are never looked up and their logits are cut off before
+    the loss, so the function computed is unchanged; the padding only lets the library GEMM of the LM
+    head use aligned tensor-core tiles (an odd vocabulary size sends cuBLAS to its legacy kernels,
+    about 9x slower on B200).  `vocab_size` rows of a reference checkpoint go into the first rows.
 """
 from __future__ import annotations
 
@@ -85,11 +90,13 @@ class TransformerLM(nn.Module):
                  attention_cls: Callable[..., nn.Module] = HierarchicalAttention,
                  span_init: Callable[[torch.Tensor], Optional[torch.Tensor]] = generate_span_input_Y):
         super().__init__()
-        self.embedding = nn.Embedding(vocab_size, d_model)
+        self.vocab_size = vocab_size
+        self.vocab_padded = (vocab_size + 63) // 64 * 64
+        self.embedding = nn.Embedding(self.vocab_padded, d_model)
         self.pos_encoding = PositionalEncoding(d_model, dropout=dropout, max_len=max_len)
         self.layers = nn.ModuleList([
             DecoderLayer(d_model, num_heads, d_ff, dropout, window_size, attention_cls) for _ in range(num_layers)])
-        self.fc_out = nn.Linear(d_model, vocab_size)
+        self.fc_out = nn.Linear(d_model, self.vocab_padded)
         self.fc_out.weight = self.embedding.weight          # weight tying, as the reference
         self.d_model = d_model
         self._span_init = span_init
@@ -114,7 +121,7 @@ class TransformerLM(nn.Module):
                 x, y, _ = layer(x, y, mask=causal_flag, return_attention=True)
             else:
                 x, y = layer(x, y, mask=causal_flag)
-        return self.fc_out(x)
+        return self.fc_out(x)[..., : self.vocab_size]
 
 
 def zipf_tokens(batch: int, length: int, vocab: int, seed: int, s: float = 1.1, device="cpu") -> torch.Tensor:

@@ -441,7 +441,7 @@ def test_language_model_against_oracle_layers(hsa):
     against the same model built around the CPU oracle layer."""
     from sparseattention_b200.lm import TransformerLM, lm_loss, zipf_tokens
     torch.backends.cuda.matmul.allow_tf32 = False
-    vocab, d, heads, ff, layers, N = 211, 64, 4, 128, 2, 64
+    vocab, d, heads, ff, layers, N = 211, 64, 4, 128, 2, 64      # 211 pads to 256 rows
     torch.manual_seed(5)
     ref = TransformerLM(vocab, d, heads, ff, layers, dropout=0.0, window_size=4,
                         attention_cls=orc.HierarchicalAttentionOracle, span_init=orc.generate_span_input_Y).eval()
