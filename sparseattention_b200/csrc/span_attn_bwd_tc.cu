@@ -128,26 +128,39 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
         stage_tree(vg, a.v_rs, Vt);
         cp_async_commit();
 
-        // delta = rowsum(dOut * Out) and log-sum-exp (base 2) of every staged query row
-        cp_async_wait<1>();
-        __syncthreads();
-        for (int i = rg; i < a.q_rows; i += RPI) {
-            const int n = q_lo + i;
-            const bool ok = (unsigned)n < (unsigned)N;
-            float part = 0.f;
-            if (ok) {
-                const uint4 ov = __ldg(reinterpret_cast<const uint4 *>(og + (int64_t)n * a.o_rs + c * 8));
-                const uint4 gv = *reinterpret_cast<const uint4 *>(Gs + i * PITCH + c * 16);
-                const T *oe = reinterpret_cast<const T *>(&ov);
-                const T *ge = reinterpret_cast<const T *>(&gv);
+        // delta = rowsum(dOut * Out) and log-sum-exp (base 2) of every staged query row.  The Out chunks and
+        // the statistics come straight from global memory; all loads of a batch are issued before anything
+        // waits (the first batch even before dOut has landed), so only one memory latency is exposed.
+        constexpr int PF = 10;                       // rows per thread in flight
+        for (int i0 = rg; i0 < a.q_rows; i0 += RPI * PF) {
+            uint4 ov[PF];
+            float lv[PF];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) part = fmaf(Traits<T>::to_f(oe[e]), Traits<T>::to_f(ge[e]), part);
+            for (int j = 0; j < PF; ++j) {
+                const int i = i0 + j * RPI;
+                const int n = q_lo + i;
+                const bool ok = i < a.q_rows && (unsigned)n < (unsigned)N;
+                ov[j] = ok ? __ldg(reinterpret_cast<const uint4 *>(og + (int64_t)n * a.o_rs + c * 8)) : make_uint4(0, 0, 0, 0);
+                lv[j] = (ok && c == 0) ? __ldg(a.lse + ((int64_t)b * N + n) * a.H + h) * 1.4426950408889634f : INFINITY;
             }
+            if (i0 == rg) { cp_async_wait<1>(); __syncthreads(); }      // dOut rows are in shared memory
 #pragma unroll
-            for (int o = CPR / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (c == 0) {
-                dl_s[i] = part;
-                lse_s[i] = ok ? a.lse[((int64_t)b * N + n) * a.H + h] * 1.4426950408889634f : INFINITY;
+            for (int j = 0; j < PF; ++j) {
+                const int i = i0 + j * RPI;
+                float part = 0.f;
+                if (i < a.q_rows) {
+                    const uint4 gv = *reinterpret_cast<const uint4 *>(Gs + i * PITCH + c * 16);
+                    const T *oe = reinterpret_cast<const T *>(&ov[j]);
+                    const T *ge = reinterpret_cast<const T *>(&gv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) part = fmaf(Traits<T>::to_f(oe[e]), Traits<T>::to_f(ge[e]), part);
+                }
+#pragma unroll
+                for (int o = CPR / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                if (c == 0 && i < a.q_rows) {
+                    dl_s[i] = part;
+                    lse_s[i] = lv[j];
+                }
             }
         }
         cp_async_wait<0>();
