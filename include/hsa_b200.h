@@ -130,6 +130,27 @@ int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const fl
                       int dtype, int algo, void *stream);
 
 /*
+ * Label-smoothed cross entropy over rows of logits whose last dimension may be padded.
+ * Replaces the criterion of the reference's training loop, nn.CrossEntropyLoss(ignore_index=pad,
+ * label_smoothing=0.1) applied to the [B*N, vocab] logits
+ * (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.py:514, 562-572).
+ *   logits  [M, >= V] with `row_stride` elements between rows; only columns [0, V) are classes
+ *   targets [M] int64; rows with targets == ignore_index give zero loss and zero gradient
+ *   loss_rows [M], lse [M] float32 outputs (the caller reduces loss_rows; "mean" divides by the
+ *   number of rows that are not ignored)
+ * Backward: dlogits [M, Vp] (same dtype) = grad_scale[0] * d loss_row / d logits; the padding
+ * columns [V, Vp) are written as zeros.  grad_scale is a DEVICE float (upstream gradient divided by
+ * the number of counted rows), so no host synchronisation is needed.
+ */
+int hsa_cross_entropy_fwd(const void *logits, int64_t row_stride, const int64_t *targets,
+                          float *loss_rows, float *lse, int64_t M, int V, float smoothing,
+                          int64_t ignore_index, int dtype, void *stream);
+int hsa_cross_entropy_bwd(const void *logits, int64_t row_stride, const int64_t *targets,
+                          const float *lse, const float *grad_scale, void *dlogits,
+                          int64_t drow_stride, int64_t M, int V, int Vp, float smoothing,
+                          int64_t ignore_index, int dtype, void *stream);
+
+/*
  * Span attention backward without any workspace argument.  No counterpart in the reference
  * project: it exists for hosts that cannot allocate device memory around the call (a plugin
  * execute hook that only receives pre-bound buffers; a server whose GPU memory is fully

@@ -273,3 +273,12 @@ class HierarchicalAttentionOracle(nn.Module):
         assert y is not None and query.size(1) == key.size(1) == value.size(1)
         out = self.update_X_from_Y(query, y, mask)
         return (out, None) if return_attention else out
+
+
+def lm_loss_reference(model, tokens, label_smoothing: float = 0.1, ignore_index: int = -100):
+    """The reference's criterion on a [B, N+1] token window: nn.CrossEntropyLoss(ignore_index, label_smoothing)
+    on logits of window[:, :-1] against window[:, 1:]
+    (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.py:181-194, 514, 562-572)."""
+    logits = model(tokens[:, :-1])
+    return F.cross_entropy(logits.reshape(-1, logits.size(-1)).float(), tokens[:, 1:].reshape(-1),
+                           label_smoothing=label_smoothing, ignore_index=ignore_index)

@@ -7,7 +7,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint8, c_void_p
+from ctypes import Structure, c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 
 import torch
 
@@ -43,6 +43,10 @@ SIGNATURES = {
     "hsa_span_attn_fwd": (c_int, [V, V, V, V, c_void_p] + [c_int] * 8 + [c_void_p]),
     "hsa_span_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 8),
     "hsa_span_attn_bwd": (c_int, [V, V, V, V, c_void_p, V, V, V, V, c_void_p, c_size_t] + [c_int] * 8 + [c_void_p]),
+    "hsa_cross_entropy_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_int64,
+                                      c_int, c_void_p]),
+    "hsa_cross_entropy_bwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int,
+                                      c_int, c_float, c_int64, c_int, c_void_p]),
     "hsa_span_attn_bwd_static": (c_int, [V, V, V, V, c_void_p, V, V, V, V] + [c_int] * 7 + [c_void_p]),
 }
 STATIC_SCRATCH_MAX_ELEMS = 1 << 20

@@ -27,6 +27,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .modules.attention import HierarchicalAttention
+from .ops.loss import cross_entropy
 from .ops.topology import generate_span_input_Y
 
 
@@ -111,7 +112,9 @@ class TransformerLM(nn.Module):
         elif isinstance(module, nn.Embedding):
             torch.nn.init.normal_(module.weight, mean=0.0, std=0.02)
 
-    def forward(self, trg, return_attention: bool = False):
+    def forward(self, trg, return_attention: bool = False, padded_logits: bool = False):
+        """Logits [B, N, vocab_size]; with padded_logits=True the [B, N, vocab_padded] tensor the LM head
+        produces (columns >= vocab_size are padding), which `lm_loss` consumes without a copy."""
         x = self.embedding(trg) * math.sqrt(self.d_model)
         x = self.pos_encoding(x)
         y = self._span_init(x)
@@ -121,7 +124,8 @@ class TransformerLM(nn.Module):
                 x, y, _ = layer(x, y, mask=causal_flag, return_attention=True)
             else:
                 x, y = layer(x, y, mask=causal_flag)
-        return self.fc_out(x)[..., : self.vocab_size]
+        logits = self.fc_out(x)
+        return logits if padded_logits else logits[..., : self.vocab_size]
 
 
 def zipf_tokens(batch: int, length: int, vocab: int, seed: int, s: float = 1.1, device="cpu") -> torch.Tensor:
@@ -132,9 +136,11 @@ def zipf_tokens(batch: int, length: int, vocab: int, seed: int, s: float = 1.1, 
     return ids.view(batch, length).to(device)
 
 
-def lm_loss(model: nn.Module, tokens: torch.Tensor, label_smoothing: float = 0.1) -> torch.Tensor:
+def lm_loss(model: "TransformerLM", tokens: torch.Tensor, label_smoothing: float = 0.1,
+            ignore_index: int = -100) -> torch.Tensor:
     """Next-token cross entropy on a [B, N+1] window: input = window[:, :-1], labels = window[:, 1:]
-    (the reference's loader and criterion, Pretrain.py:181-194, 514)."""
-    logits = model(tokens[:, :-1])
-    return F.cross_entropy(logits.reshape(-1, logits.size(-1)).float(), tokens[:, 1:].reshape(-1),
-                           label_smoothing=label_smoothing)
+    (the reference's loader and criterion, Pretrain.py:181-194, 514), computed by the library's
+    cross-entropy kernel straight on the padded logits."""
+    logits = model(tokens[:, :-1], padded_logits=True)
+    return cross_entropy(logits.reshape(-1, logits.size(-1)), tokens[:, 1:].reshape(-1), model.vocab_size,
+                         label_smoothing=label_smoothing, ignore_index=ignore_index)

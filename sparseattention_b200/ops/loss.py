@@ -1,0 +1,68 @@
+"""Label-smoothed cross entropy on (column-padded) logits, backed by the CUDA library.
+
+Stands in for `nn.CrossEntropyLoss(ignore_index=..., label_smoothing=...)` as the reference's training
+loop uses it (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.py:514, 562-572), with one
+addition: the logits may carry padding columns beyond `num_classes` (the LM pads its vocabulary matrix
+so the LM-head GEMM stays on aligned tensor-core tiles); they are excluded from the softmax and get
+zero gradient.  The logits are read once forward and once backward, in their own dtype.
+"""
+from __future__ import annotations
+
+from ctypes import c_void_p
+
+import torch
+
+from .. import _lib
+
+
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, num_classes, label_smoothing, ignore_index):
+        lib = _lib.load()
+        dev = _lib.require_cuda(logits, targets)
+        assert logits.dim() == 2 and targets.dim() == 1 and targets.numel() == logits.size(0)
+        assert targets.dtype == torch.int64, "targets must be int64"
+        if logits.stride(1) != 1:
+            logits = logits.contiguous()
+        targets = targets.contiguous()
+        M, Vp = logits.shape
+        V = int(num_classes)
+        assert 1 <= V <= Vp
+        loss_rows = torch.empty(M, dtype=torch.float32, device=dev)
+        lse = torch.empty(M, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = lib.hsa_cross_entropy_fwd(c_void_p(logits.data_ptr()), logits.stride(0), c_void_p(targets.data_ptr()),
+                                           c_void_p(loss_rows.data_ptr()), c_void_p(lse.data_ptr()), M, V,
+                                           float(label_smoothing), int(ignore_index), _lib.dtype_code(logits),
+                                           _lib.stream_ptr(dev))
+        _lib.check(rc, "hsa_cross_entropy_fwd")
+        count = (targets != ignore_index).sum().clamp_min(1).to(torch.float32)
+        ctx.save_for_backward(logits, targets, lse, count)
+        ctx.meta = (V, float(label_smoothing), int(ignore_index))
+        return loss_rows.sum() / count
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        lib = _lib.load()
+        logits, targets, lse, count = ctx.saved_tensors
+        V, eps, ignore = ctx.meta
+        dev = logits.device
+        M, Vp = logits.shape
+        scale = (grad_out.to(torch.float32) / count).reshape(1).contiguous()
+        dlogits = torch.empty_like(logits)
+        with torch.cuda.device(dev):
+            rc = lib.hsa_cross_entropy_bwd(c_void_p(logits.data_ptr()), logits.stride(0), c_void_p(targets.data_ptr()),
+                                           c_void_p(lse.data_ptr()), c_void_p(scale.data_ptr()),
+                                           c_void_p(dlogits.data_ptr()), dlogits.stride(0), M, V, Vp, eps, ignore,
+                                           _lib.dtype_code(logits), _lib.stream_ptr(dev))
+        _lib.check(rc, "hsa_cross_entropy_bwd")
+        return dlogits, None, None, None, None
+
+
+def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, num_classes: int | None = None,
+                  label_smoothing: float = 0.0, ignore_index: int = -100) -> torch.Tensor:
+    """Mean label-smoothed cross entropy.  logits [M, Vp] (columns >= num_classes are padding),
+    targets [M] int64.  Same value and gradient as F.cross_entropy(logits[:, :num_classes].float(), ...)."""
+    if num_classes is None:
+        num_classes = logits.size(-1)
+    return _CrossEntropy.apply(logits, targets, num_classes, label_smoothing, ignore_index)

@@ -450,7 +450,7 @@ def test_language_model_against_oracle_layers(hsa):
     ours.load_state_dict(ref.state_dict())
     ours = ours.cuda()
     tokens = zipf_tokens(2, N + 1, vocab, seed=9)
-    lr = lm_loss(ref, tokens)
+    lr = orc.lm_loss_reference(ref, tokens)
     lr.backward()
     lo = lm_loss(ours, tokens.cuda())
     lo.backward()
@@ -461,3 +461,24 @@ def test_language_model_against_oracle_layers(hsa):
         g_ours = dict(ours.named_parameters())[name].grad.cpu()
         g_ref = dict(ref.named_parameters())[name].grad
         assert rel_err(g_ours, g_ref) < 2e-5, name
+
+
+@pytest.mark.parametrize("M,V,Vp", [(7, 5, 5), (33, 211, 256), (16, 50257, 50304), (4, 1000, 1001)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("eps", [0.0, 0.1])
+def test_cross_entropy_vs_torch(hsa, M, V, Vp, dtype, eps):
+    from sparseattention_b200.ops.loss import cross_entropy
+    gen = torch.Generator().manual_seed(M + V)
+    logits = (torch.randn(M, Vp, generator=gen) * 3).to(dtype)
+    targets = torch.randint(0, V, (M,), generator=gen)
+    targets[0] = -100                                   # an ignored row
+    ref_in = logits[:, :V].double().clone().requires_grad_()          # float64 on the same rounded logits
+    ref = torch.nn.functional.cross_entropy(ref_in, targets, label_smoothing=eps, ignore_index=-100)
+    ref.backward()
+    x = logits.cuda().requires_grad_()
+    out = cross_entropy(x, targets.cuda(), V, label_smoothing=eps, ignore_index=-100)
+    out.backward()
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert abs(float(out.detach()) - float(ref.detach())) <= 1e-5 * abs(float(ref.detach())) + 1e-6
+    assert rel_err(x.grad[:, :V].float().cpu(), ref_in.grad) < tol
+    assert float(x.grad[:, V:].abs().sum()) == 0.0 and float(x.grad[0].abs().sum()) == 0.0
