@@ -13,6 +13,8 @@
 // registers (quad shuffles), and multiplies by V through ldmatrix.trans.  The level-0 sibling n^1 lies
 // inside the window; where both slots are valid its probability counts twice (reference semantics),
 // done by adding 1 to its base-2 logit.
+#include <cstdlib>
+
 #include "tc_common.cuh"
 
 namespace hsa {
@@ -26,6 +28,7 @@ struct SpanTcArgs {
     int RB;          // ceil(R / 16)
     int band_rows;   // leaf rows staged per tile
     int kv_rows;     // all rows staged per tile
+    int pf_dist;     // L2 prefetch distance in work items (0 = off)
     float scale_log2e;
 };
 
@@ -42,9 +45,12 @@ span_fwd_tc_kernel(SpanTcArgs a) {
     unsigned char *Vs = Ks + (size_t)a.kv_rows * PITCH;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // work item id -> (batch, tile, head); heads vary fastest so that CTAs running together touch
+    // neighbouring 2*D-byte pieces of the same rows
+    const int ntiles = a.N / kTile;
     const int h = blockIdx.x % a.H;
-    const int tile = blockIdx.x / a.H;
-    const int b = blockIdx.y;
+    const int tile = (blockIdx.x / a.H) % ntiles;
+    const int b = blockIdx.x / (a.H * ntiles);
     const int t0 = tile * kTile;
     const int N = a.N, L = a.L, R = a.R, RB = a.RB;
     const int band_lo = t0 - 16 * RB;
@@ -104,6 +110,46 @@ span_fwd_tc_kernel(SpanTcArgs a) {
         cp_async_commit();
         stage_kv(vg, a.v_rs, Vs);
         cp_async_commit();
+
+        // Pull the working set of a work item that will start about one CTA lifetime from now into L2
+        // (one prefetch per 128 bytes), so that its own staging finds the rows on chip: HBM latency is
+        // then hidden behind a whole tile period instead of being paid inside every CTA.
+        const int64_t nid = (int64_t)blockIdx.x + a.pf_dist;
+        if (a.pf_dist > 0 && nid < (int64_t)gridDim.x && (c & 7) == 0) {
+            const int ph = (int)(nid % a.H);
+            const int pt0 = (int)((nid / a.H) % ntiles) * kTile;
+            const int pb = (int)(nid / ((int64_t)a.H * ntiles));
+            const int64_t ho = (int64_t)ph * D + c * 8;
+            const T *pk = (const T *)a.k + pb * a.k_bs + ho;
+            const T *pv = (const T *)a.v + pb * a.v_bs + ho;
+            const T *pq = (const T *)a.q + pb * a.q_bs + ho;
+            for (int i = rg; i < a.band_rows; i += RPI) {
+                const int r = pt0 - 16 * RB + i;
+                if ((unsigned)r < (unsigned)N) {
+                    prefetch_l2(pk + (int64_t)r * a.k_rs);
+                    prefetch_l2(pv + (int64_t)r * a.v_rs);
+                }
+            }
+            for (int f = rg; f < ntree; f += RPI) {
+                int rr;
+                bool ok = true;
+                if (f < TIN) {
+                    const int rem = (CAUSAL ? 32 : 64) - f;
+                    const int l = (CAUSAL ? 5 : 6) - (31 - __clz(rem - 1));
+                    const int i = f - tree_level_off<CAUSAL>(l);
+                    rr = level_base(N, l) + (pt0 >> l) + (CAUSAL ? 2 * i : i);
+                } else {
+                    const int l = kTileLog + (f - TIN);
+                    ok = !CAUSAL || ((pt0 >> l) & 1);
+                    rr = level_base(N, l) + ((pt0 >> l) ^ 1);
+                }
+                if (ok) {
+                    prefetch_l2(pk + (int64_t)rr * a.k_rs);
+                    prefetch_l2(pv + (int64_t)rr * a.v_rs);
+                }
+            }
+            for (int i = rg; i < kTile; i += RPI) prefetch_l2(pq + (int64_t)(pt0 + i) * a.q_rs);
+        }
     }
 
     const int nbb = CAUSAL ? RB + 1 : 2 * RB + 1;
@@ -290,11 +336,21 @@ template <typename T, int D>
 static int launch_tc(const SpanTcArgs &a, int B, bool causal, cudaStream_t st) {
     constexpr int PITCH = D * 2 + 16;
     const size_t smem = (size_t)(2 * a.kv_rows) * PITCH;
-    dim3 grid((unsigned)((a.N / kTile) * a.H), (unsigned)B);
+    const int64_t total = (int64_t)B * (a.N / kTile) * a.H;
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_fwd(tc): shared memory %zu: %s", smem, cudaGetErrorString(e));
-        kernel<<<grid, 128, smem, st>>>(a);
+        // prefetch distance = the number of CTAs resident on the device: CTAs start in index order, so the
+        // item that far ahead is the one that takes this CTA's place
+        int dev = 0, sms = 0, per_sm = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        SpanTcArgs args = a;
+        args.pf_dist = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 128, smem) == cudaSuccess && per_sm > 0 && sms > 0)
+            args.pf_dist = per_sm * sms;
+        if (const char *env = getenv("HSA_FWD_PREFETCH")) args.pf_dist = atoi(env);
+        kernel<<<(unsigned)total, 128, smem, st>>>(args);
         return launch_status("hsa_span_attn_fwd(tc)");
     };
     return causal ? go(span_fwd_tc_kernel<T, D, true>) : go(span_fwd_tc_kernel<T, D, false>);
@@ -311,7 +367,7 @@ bool hsa_span_attn_fwd_tc_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_view
     if (D != 64 && D != 128) return false;
     if (N < kTile || (N & (N - 1)) != 0 || N > (1 << 28)) return false;
     if (B < 1 || B > 65535 || H < 1 || radius < 0) return false;
-    if ((int64_t)(N / kTile) * H > 0x7fffffffLL) return false;
+    if ((int64_t)(N / kTile) * H * B > 0x7fffffffLL) return false;      // one CTA per work item, 1-D grid
     if (!view_vec_ok(Q, 2) || !view_vec_ok(K, 2) || !view_vec_ok(V, 2) || !view_vec_ok(Out, 2)) return false;
     const int R = radius < N ? radius : N;
     const int RB = (R + 15) / 16;
