@@ -13,8 +13,6 @@
 // registers (quad shuffles), and multiplies by V through ldmatrix.trans.  The level-0 sibling n^1 lies
 // inside the window; where both slots are valid its probability counts twice (reference semantics),
 // done by adding 1 to its base-2 logit.
-#include <cstdlib>
-
 #include "tc_common.cuh"
 
 namespace hsa {
@@ -28,7 +26,6 @@ struct SpanTcArgs {
     int RB;          // ceil(R / 16)
     int band_rows;   // leaf rows staged per tile
     int kv_rows;     // all rows staged per tile
-    int pf_dist;     // L2 prefetch distance in work items (0 = off)
     float scale_log2e;
 };
 
@@ -110,46 +107,6 @@ span_fwd_tc_kernel(SpanTcArgs a) {
         cp_async_commit();
         stage_kv(vg, a.v_rs, Vs);
         cp_async_commit();
-
-        // Pull the working set of a work item that will start about one CTA lifetime from now into L2
-        // (one prefetch per 128 bytes), so that its own staging finds the rows on chip: HBM latency is
-        // then hidden behind a whole tile period instead of being paid inside every CTA.
-        const int64_t nid = (int64_t)blockIdx.x + a.pf_dist;
-        if (a.pf_dist > 0 && nid < (int64_t)gridDim.x && (c & 7) == 0) {
-            const int ph = (int)(nid % a.H);
-            const int pt0 = (int)((nid / a.H) % ntiles) * kTile;
-            const int pb = (int)(nid / ((int64_t)a.H * ntiles));
-            const int64_t ho = (int64_t)ph * D + c * 8;
-            const T *pk = (const T *)a.k + pb * a.k_bs + ho;
-            const T *pv = (const T *)a.v + pb * a.v_bs + ho;
-            const T *pq = (const T *)a.q + pb * a.q_bs + ho;
-            for (int i = rg; i < a.band_rows; i += RPI) {
-                const int r = pt0 - 16 * RB + i;
-                if ((unsigned)r < (unsigned)N) {
-                    prefetch_l2(pk + (int64_t)r * a.k_rs);
-                    prefetch_l2(pv + (int64_t)r * a.v_rs);
-                }
-            }
-            for (int f = rg; f < ntree; f += RPI) {
-                int rr;
-                bool ok = true;
-                if (f < TIN) {
-                    const int rem = (CAUSAL ? 32 : 64) - f;
-                    const int l = (CAUSAL ? 5 : 6) - (31 - __clz(rem - 1));
-                    const int i = f - tree_level_off<CAUSAL>(l);
-                    rr = level_base(N, l) + (pt0 >> l) + (CAUSAL ? 2 * i : i);
-                } else {
-                    const int l = kTileLog + (f - TIN);
-                    ok = !CAUSAL || ((pt0 >> l) & 1);
-                    rr = level_base(N, l) + ((pt0 >> l) ^ 1);
-                }
-                if (ok) {
-                    prefetch_l2(pk + (int64_t)rr * a.k_rs);
-                    prefetch_l2(pv + (int64_t)rr * a.v_rs);
-                }
-            }
-            for (int i = rg; i < kTile; i += RPI) prefetch_l2(pq + (int64_t)(pt0 + i) * a.q_rs);
-        }
     }
 
     const int nbb = CAUSAL ? RB + 1 : 2 * RB + 1;
@@ -340,17 +297,7 @@ static int launch_tc(const SpanTcArgs &a, int B, bool causal, cudaStream_t st) {
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_fwd(tc): shared memory %zu: %s", smem, cudaGetErrorString(e));
-        // prefetch distance = the number of CTAs resident on the device: CTAs start in index order, so the
-        // item that far ahead is the one that takes this CTA's place
-        int dev = 0, sms = 0, per_sm = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        SpanTcArgs args = a;
-        args.pf_dist = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 128, smem) == cudaSuccess && per_sm > 0 && sms > 0)
-            args.pf_dist = per_sm * sms;
-        if (const char *env = getenv("HSA_FWD_PREFETCH")) args.pf_dist = atoi(env);
-        kernel<<<(unsigned)total, 128, smem, st>>>(args);
+        kernel<<<(unsigned)total, 128, smem, st>>>(a);
         return launch_status("hsa_span_attn_fwd(tc)");
     };
     return causal ? go(span_fwd_tc_kernel<T, D, true>) : go(span_fwd_tc_kernel<T, D, false>);

@@ -176,3 +176,52 @@ def hierarchical_attention(Q, K, V, idx_table, gather_table, mask_table=None, wi
     `mask_table` not None selects the causal variant.
     """
     return HierarchicalAttentionFunc.apply(Q, K, V, idx_table, gather_table, mask_table, window_size)
+
+
+# ---------------------------------------------------------------------------------------------
+# Host-resident inputs (inference): copy in, compute and copy out overlapped over batch chunks
+# ---------------------------------------------------------------------------------------------
+_host_streams: Dict[int, Tuple[torch.cuda.Stream, torch.cuda.Stream]] = {}
+
+
+def hierarchical_attention_from_host(Q, K, V, window_size=16, is_causal=True, out=None, device=None, chunks=8):
+    """Span attention on HOST tensors (pinned memory recommended): Q [B,N,H,D], K,V [B,2N-1,H,D].
+
+    The batch is cut into `chunks` pieces; piece i+1 is copied to the device while piece i is computed and
+    piece i-1 is copied back, so the call costs about max(copy-in, copy-out, compute) instead of their
+    sum.  Returns a host tensor [B,N,H,D] (`out` if given; pinned otherwise).  No autograd.
+    """
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    B, N, H, D = Q.shape
+    assert not Q.is_cuda and not K.is_cuda and not V.is_cuda, "inputs of this entry point live on the host"
+    assert K.shape == (B, 2 * N - 1, H, D) and V.shape == K.shape
+    if out is None:
+        out = torch.empty((B, N, H, D), dtype=Q.dtype).pin_memory()
+    if dev.index not in _host_streams:
+        _host_streams[dev.index] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    work, back = _host_streams[dev.index]
+    nchunk = max(1, min(int(chunks), B))
+    bounds = [(B * i) // nchunk for i in range(nchunk + 1)]
+    cur = torch.cuda.current_stream(dev)
+    work.wait_stream(cur)
+    back.wait_stream(cur)
+    keep = []
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        if hi == lo:
+            continue
+        with torch.cuda.stream(work):
+            q = Q[lo:hi].to(dev, non_blocking=True)
+            k = K[lo:hi].to(dev, non_blocking=True)
+            v = V[lo:hi].to(dev, non_blocking=True)
+            o, _ = span_attention_forward(q, k, v, window_size, is_causal, need_lse=False)
+            done = torch.cuda.Event()
+            done.record(work)
+        with torch.cuda.stream(back):
+            back.wait_event(done)
+            out[lo:hi].copy_(o, non_blocking=True)
+        keep.append((q, k, v, o))
+    cur.wait_stream(back)
+    for tensors in keep:                      # the caching allocator must not hand these out before `cur` passes
+        for t in tensors:
+            t.record_stream(cur)
+    return out

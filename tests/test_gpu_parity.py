@@ -482,3 +482,18 @@ def test_cross_entropy_vs_torch(hsa, M, V, Vp, dtype, eps):
     assert abs(float(out.detach()) - float(ref.detach())) <= 1e-5 * abs(float(ref.detach())) + 1e-6
     assert rel_err(x.grad[:, :V].float().cpu(), ref_in.grad) < tol
     assert float(x.grad[:, V:].abs().sum()) == 0.0 and float(x.grad[0].abs().sum()) == 0.0
+
+
+def test_host_entry_point_matches_device_path(hsa):
+    """hierarchical_attention_from_host (chunked, stream-overlapped) gives the device path's bits."""
+    from sparseattention_b200.ops import functional as F
+    gen = torch.Generator().manual_seed(4)
+    B, N, H, D, R = 5, 256, 4, 64, 8
+    Q = torch.randn(B, N, H, D, generator=gen).bfloat16().pin_memory()
+    K = torch.randn(B, 2 * N - 1, H, D, generator=gen).bfloat16().pin_memory()
+    V = torch.randn(B, 2 * N - 1, H, D, generator=gen).bfloat16().pin_memory()
+    want, _ = F.span_attention_forward(Q.cuda(), K.cuda(), V.cuda(), R, True, need_lse=False)
+    for chunks in (1, 2, 8):
+        got = F.hierarchical_attention_from_host(Q, K, V, R, True, chunks=chunks)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want.cpu())
