@@ -37,6 +37,10 @@ bool hsa_span_attn_fwd_tc_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_view
 int hsa_span_attn_fwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H, int D,
                          int radius, int causal, int dtype, cudaStream_t st);
 
+bool hsa_span_attn_fwd_tc128_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, int B, int N, int H, int D,
+                                       int radius, int causal, int dtype);
+int hsa_span_attn_fwd_tc128(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H, int D,
+                            int radius, int causal, int dtype, cudaStream_t st);
 bool hsa_span_attn_bwd_tc_supported(const hsa_view *views, int nviews, int B, int N, int H, int D, int radius,
                                     int causal, int dtype);
 size_t hsa_span_attn_bwd_tc_workspace(int B, int N, int H, int D);
@@ -59,7 +63,12 @@ extern "C" int hsa_compiled_arch(void) {
 extern "C" int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N,
                                  int H, int D, int radius, int causal, int dtype, int algo, void *stream) {
     HSA_CHECK_ARG(Q.ptr && K.ptr && V.ptr && Out.ptr, "hsa_span_attn_fwd: null pointer");
-    HSA_CHECK_ARG(algo >= 0 && algo <= 2, "hsa_span_attn_fwd: unknown algo %d", algo);
+    HSA_CHECK_ARG(algo >= 0 && algo <= 4, "hsa_span_attn_fwd: unknown algo %d", algo);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (algo == 4) return hsa_span_attn_fwd_tc128(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, st);
+    if (algo == 3) return hsa_span_attn_fwd_tc(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, st);
+    if (algo != 1 && hsa_span_attn_fwd_tc128_supported(Q, K, V, Out, B, N, H, D, radius, causal, dtype))
+        return hsa_span_attn_fwd_tc128(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, st);
     if (algo == 2 || (algo == 0 && hsa_span_attn_fwd_tc_supported(Q, K, V, Out, B, N, H, D, radius, causal, dtype)))
         return hsa_span_attn_fwd_tc(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, (cudaStream_t)stream);
     return hsa_span_attn_fwd_generic(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, (cudaStream_t)stream);
@@ -74,7 +83,7 @@ extern "C" size_t hsa_span_attn_bwd_workspace_bytes(int B, int N, int H, int D, 
     const bool tc_dtype = (dtype == HSA_BF16 || dtype == HSA_F16) && (D == 64 || D == 128) && N >= 64;
     const size_t tc = tc_dtype ? hsa_span_attn_bwd_tc_workspace(B, N, H, D) : 0;
     if (algo == 1) return portable;
-    if (algo == 2) return tc;
+    if (algo >= 2) return tc;
     return portable > tc ? portable : tc;
 }
 
@@ -84,7 +93,7 @@ extern "C" int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Ou
                                  int dtype, int algo, void *stream) {
     HSA_CHECK_ARG(Q.ptr && K.ptr && V.ptr && Out.ptr && LSE && dOut.ptr && dQ.ptr && dK.ptr && dV.ptr,
                   "hsa_span_attn_bwd: null pointer");
-    HSA_CHECK_ARG(algo >= 0 && algo <= 2, "hsa_span_attn_bwd: unknown algo %d", algo);
+    HSA_CHECK_ARG(algo >= 0 && algo <= 4, "hsa_span_attn_bwd: unknown algo %d", algo);
     const size_t need = hsa_span_attn_bwd_workspace_bytes(B, N, H, D, radius, causal, dtype, algo);
     if (workspace == nullptr || workspace_bytes < need)
         return fail(HSA_ERR_WORKSPACE, "hsa_span_attn_bwd: workspace of %zu bytes needed, %zu given", need,
@@ -92,7 +101,7 @@ extern "C" int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Ou
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
         return fail(HSA_ERR_ALIGN, "hsa_span_attn_bwd: workspace must be 256-byte aligned");
     const hsa_view views[] = {Q, K, V, Out, dOut, dQ, dK, dV};
-    if (algo == 2 || (algo == 0 && hsa_span_attn_bwd_tc_supported(views, 8, B, N, H, D, radius, causal, dtype)))
+    if (algo >= 2 || (algo == 0 && hsa_span_attn_bwd_tc_supported(views, 8, B, N, H, D, radius, causal, dtype)))
         return hsa_span_attn_bwd_tc(Q, K, V, Out, LSE, dOut, dQ, dK, dV, workspace, B, N, H, D, radius, causal, dtype,
                                     (cudaStream_t)stream);
     return hsa_span_attn_bwd_generic(Q, K, V, Out, LSE, dOut, dQ, dK, dV, workspace, B, N, H, D, radius, causal,

@@ -56,7 +56,7 @@ def test_bad_arguments_return_codes():
     assert lib.hsa_span_attn_fwd(_v(), _v(), _v(), _v(), None, 1, 12, 1, 16, 1, 1, 0, 0, None) == -1
     assert lib.hsa_span_attn_fwd(_v(0), _v(), _v(), _v(), None, 1, 16, 1, 16, 1, 1, 0, 0, None) == -1
     assert lib.hsa_span_attn_fwd(_v(), _v(), _v(), _v(), None, 1, 16, 1, 16, 1, 1, 7, 0, None) == -3
-    assert lib.hsa_span_attn_fwd(_v(), _v(), _v(), _v(), None, 1, 16, 1, 16, 1, 1, 0, 9, None) == -1
+    assert lib.hsa_span_attn_fwd(_v(), _v(), _v(), _v(), None, 1, 16, 1, 16, 1, 1, 0, 9, None) == -1   # unknown algo
     assert lib.hsa_span_attn_fwd(_v(), _v(), _v(), _v(), None, 1, 16, 1, 16, -1, 1, 0, 0, None) == -1
     assert lib.hsa_span_attn_fwd(_v(), _v(), _v(), _v(), None, 1, 16, 1, 100000, 1, 1, 0, 0, None) == -1
     # parent op: zero parents

@@ -234,6 +234,16 @@ def test_span_attention_tensor_core(hsa, case, causal, dtype):
     run_span_case(hsa, *case, causal, dtype, algo=2)
 
 
+@pytest.mark.parametrize("case", [(1, 128, 1, 64, 0), (2, 128, 3, 64, 5), (1, 256, 2, 128, 16), (2, 1024, 3, 64, 8),
+                                  (1, 4096, 2, 128, 16), (1, 8192, 1, 128, 7), (3, 512, 5, 128, 1)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_span_attention_tensor_core_128_leaf_tiles(hsa, case, dtype):
+    """The 128-leaf-tile forward (algo 4, causal) against the oracle, and bit-for-bit LSE agreement is not
+    required between tile sizes, only the common tolerance."""
+    run_span_case(hsa, *case, True, dtype, algo=4, check_grad=False)
+    run_span_case(hsa, *case, True, dtype, algo=3, check_grad=False)
+
+
 def test_tensor_core_kernel_refuses_what_it_cannot_take(hsa):
     from sparseattention_b200._lib import HsaError
     from sparseattention_b200.ops import functional as F
@@ -246,6 +256,12 @@ def test_tensor_core_kernel_refuses_what_it_cannot_take(hsa):
     with pytest.raises(HsaError):
         F.span_attention_forward(q, kv, kv, 4, True, algo=2)
     F.span_attention_forward(q, kv, kv, 4, True, algo=0)                          # automatic choice still works
+    qb = torch.randn(1, 128, 1, 64, device="cuda", dtype=torch.bfloat16)
+    kvb = torch.randn(1, 255, 1, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(HsaError):
+        F.span_attention_forward(qb, kvb, kvb, 17, True, algo=4)                 # radius beyond the 128-leaf kernel
+    with pytest.raises(HsaError):
+        F.span_attention_forward(qb, kvb, kvb, 4, False, algo=4)                 # not causal
 
 
 def test_span_attention_rejects_foreign_tables(hsa):
