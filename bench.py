@@ -411,6 +411,32 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_sweep(args):
+    """BASELINE config 5: forward-only bf16 sweep over N and batch (H=16, D=128, causal, radius 16 and 32).
+    Prints a markdown table: achieved algorithmic GB/s and fraction of the measured HBM copy bandwidth."""
+    from sparseattention_b200.ops import functional as F
+    torch.cuda.set_device(0)
+    peak, kind = measured_peaks()
+    H, D = 16, 128
+    print(f"| N | B | radius | ms | tokens/s | GB/s (algorithmic) | of {kind} {peak:.0f} GB/s | footprint MB |")
+    print("|---|---|---|---|---|---|---|---|")
+    for N in (1024, 2048, 4096, 8192, 16384, 32768):
+        for B in (1, 8, 32):
+            if 6 * B * N * H * D * 2 > 40e9:
+                continue
+            gen = torch.Generator(device="cuda").manual_seed(N + B)
+            Q = torch.randn(B, N, H, D, generator=gen, device="cuda", dtype=torch.bfloat16)
+            K = torch.randn(B, 2 * N - 1, H, D, generator=gen, device="cuda", dtype=torch.bfloat16)
+            V = torch.randn(B, 2 * N - 1, H, D, generator=gen, device="cuda", dtype=torch.bfloat16)
+            for R in (16, 32):
+                ms = time_cuda(lambda: F.span_attention_forward(Q, K, V, R, True, need_lse=False), 30, 5, lambda: None) / 30
+                alg = algorithmic_bytes_fwd(B, N, H, D, 2, True)
+                gbs = alg / (ms * 1e-3) / 1e9
+                foot = 6 * B * N * H * D * 2 / 1e6
+                print(f"| {N} | {B} | {R} | {ms:.4f} | {B * N / (ms * 1e-3):.3e} | {gbs:.0f} | {gbs / peak:.3f} | {foot:.0f} |")
+            del Q, K, V
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -423,7 +449,11 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-lm", action="store_true")
     ap.add_argument("--lm", default="lm_8x4096", choices=sorted(LM_CONFIGS))
+    ap.add_argument("--sweep", action="store_true", help="print the forward sweep over N and batch instead of the JSON line")
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

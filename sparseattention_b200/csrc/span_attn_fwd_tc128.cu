@@ -1,13 +1,14 @@
 // Span attention forward, tensor cores, 128-leaf tiles: the variant for the common causal case
-// (radius <= 16, N <= 8192, bf16 / f16, head dim 64 or 128, N >= 128).
+// (radius <= 16, bf16 / f16, head dim 64 or 128, N >= 128).
 //
 // Same algorithm as span_attn_fwd_tc.cu, but a CTA covers 128 leaves with 8 warps and keeps its K/V rows
 // at an unpadded pitch of 2*D bytes with the 16-byte pieces XOR-swizzled by the row (so ldmatrix stays
 // conflict free without the padding).  What that buys: 108.5 KB of staging per CTA, two CTAs = 217 KB of
 // the SM's shared memory acting as load buffers (the forward is bound by bytes in flight), 16 warps per SM
 // instead of 12, and half the halo rows per leaf.  To stay under 128 registers per thread (two CTAs of 256
-// threads) the kernel handles exactly the one-chunk case: at most two band blocks and one tree block per
-// warp, softmax without rescaling, probabilities normalised before P.V so the accumulators are final.
+// threads) the kernel scores all of a warp's key blocks first (at most two band blocks plus one tree block,
+// or two tree blocks once N > 8192), runs one softmax without rescaling, and normalises the probabilities
+// before P.V so the accumulators are final: the Q fragments are dead before the output accumulators live.
 #include "tc_common.cuh"
 
 namespace hsa {
@@ -48,7 +49,7 @@ __device__ __forceinline__ int tree_slot128(int s, int w, int L, int &row, int &
     return l;
 }
 
-template <typename T, int D>
+template <typename T, int D, int NB>      // NB: key blocks per warp the code is unrolled for (3 or 4)
 __global__ void __launch_bounds__(256, 2)
 span_fwd_tc128_kernel(SpanTc128Args a) {
     constexpr int PITCH = D * 2;
@@ -122,45 +123,48 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
     }
 
     const int nbb = RB + 1;                 // band blocks: [the warp's own 16 leaves] (+ the 16 before them)
-    const int nblk = nbb + 1;               // + one tree block
+    const int ntb = (L + 3 + 15) >> 4;      // tree blocks: 7 slots of levels 1..3 + one slot per level 4..L-1
+    const int nblk = nbb + ntb;             // <= NB (checked by the launcher)
 
     // ---------------------------------------------------------------- masks (closed-form topology)
-    uint32_t tree_bits = 0;                 // bit nt*4 + e: this thread's score element of the tree block is attended
+    uint32_t tree_bits = 0;                 // bit tb*8 + nt*4 + e: this thread's score element of tree block tb is attended
+    for (int tb = 0; tb < ntb; ++tb) {
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int slot = nt * 8 + 2 * quad + (e & 1);
-            const int i = qrow + 8 * (e >> 1);
-            int row, jj;
-            const int l = tree_slot128(slot, warp, L, row, jj);
-            bool ok = false;
-            if (l >= 1 && l <= 3) ok = (i >> l) == jj + 1;
-            else if (l >= 4) ok = ((t0 + lw) >> l) & 1;
-            tree_bits |= (ok ? 1u : 0u) << (nt * 4 + e);
-        }
+            for (int e = 0; e < 4; ++e) {
+                const int slot = 16 * tb + nt * 8 + 2 * quad + (e & 1);
+                const int i = qrow + 8 * (e >> 1);
+                int row, jj;
+                const int l = tree_slot128(slot, warp, L, row, jj);
+                bool ok = false;
+                if (l >= 1 && l <= 3) ok = (i >> l) == jj + 1;
+                else if (l >= 4) ok = ((t0 + lw) >> l) & 1;
+                tree_bits |= (ok ? 1u : 0u) << (tb * 8 + nt * 4 + e);
+            }
+    }
     const int dbase = 2 * quad - qrow;
     const bool odd = qrow & 1;              // odd leaves see their level-0 sibling (the leaf before them)
 
-    // shared-memory row of key kk (0..15) of block o: 0 = own leaves, 1 = the 16 leaves before (when RB = 1), last = tree
+    // shared-memory row of key kk (0..15) of block o: 0 = own leaves, 1 = the 16 leaves before (when RB = 1), then tree blocks
     auto key_row = [&](int o, int kk) -> int {
         if (o < nbb) return lw + 16 * (o == 0 ? RB : 0) + kk;
         int row, jj;
-        tree_slot128(kk, warp, L, row, jj);
+        tree_slot128(16 * (o - nbb) + kk, warp, L, row, jj);
         return a.band_rows + row;
     };
 
     cp_async_wait<1>();
     __syncthreads();
 
-    // ---------------------------------------------------------------- scores: 3 blocks x 2 n-tiles advance together
+    // ---------------------------------------------------------------- scores: NB blocks x 2 n-tiles advance together
     const float c2 = a.scale_log2e;
-    float s[3][2][4];
+    float s[NB][2][4];
     {
-        uint32_t kb[3];
-        int ksw[3];
+        uint32_t kb[NB];
+        int ksw[NB];
 #pragma unroll
-        for (int bi = 0; bi < 3; ++bi) {
+        for (int bi = 0; bi < NB; ++bi) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[bi][0][e] = s[bi][1][e] = 0.f;
             const int krow = key_row(min(bi, nblk - 1), (lane & 7) + 8 * (lane >> 4));
@@ -170,7 +174,7 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
-            for (int bi = 0; bi < 3; ++bi) {
+            for (int bi = 0; bi < NB; ++bi) {
                 uint32_t kf[4];
                 ldmatrix_x4(kf, kb[bi] + ((((2 * ks) & 7) ^ ksw[bi]) | ((2 * ks) & 8)) * 16);
                 mma16816<T>(s[bi][0], qf[ks], kf[0], kf[1]);
@@ -180,7 +184,7 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
     }
     // ---- masks and base-2 logits
 #pragma unroll
-    for (int bi = 0; bi < 3; ++bi) {
+    for (int bi = 0; bi < NB; ++bi) {
         if (bi < nbb) {
             const int blk = (bi == 0) ? RB : 0;                   // band block index, 0 = leftmost
             const int r0 = t0 + lw + 16 * (blk - RB);
@@ -196,12 +200,13 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
                     const float bias = (wv && lv) ? 1.f : ((wv || lv) ? 0.f : -INFINITY);
                     s[bi][nt][e] = fmaf(s[bi][nt][e], c2, bias);
                 }
-        } else if (bi == nbb) {
+        } else if (bi < nblk) {
+            const uint32_t bits = tree_bits >> (8 * (bi - nbb));
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    s[bi][nt][e] = ((tree_bits >> (nt * 4 + e)) & 1u) ? s[bi][nt][e] * c2 : -INFINITY;
+                    s[bi][nt][e] = ((bits >> (nt * 4 + e)) & 1u) ? s[bi][nt][e] * c2 : -INFINITY;
         } else {
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[bi][0][e] = s[bi][1][e] = -INFINITY;
@@ -210,7 +215,7 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
     // ---- softmax over the whole (single) chunk
     float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-    for (int bi = 0; bi < 3; ++bi)
+    for (int bi = 0; bi < NB; ++bi)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             m0 = fmaxf(m0, fmaxf(s[bi][nt][0], s[bi][nt][1]));
@@ -222,7 +227,7 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
     m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
     float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-    for (int bi = 0; bi < 3; ++bi)
+    for (int bi = 0; bi < NB; ++bi)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             s[bi][nt][0] = fast_exp2(s[bi][nt][0] - m0);
@@ -242,9 +247,9 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
         a.lse[((int64_t)b * N + n0) * a.H + h] = (m0 + log2f(l0)) * kLn2;
         a.lse[((int64_t)b * N + n1) * a.H + h] = (m1 + log2f(l1)) * kLn2;
     }
-    uint32_t pa[3][4];                       // normalised probabilities as A operands
+    uint32_t pa[NB][4];                      // normalised probabilities as A operands
 #pragma unroll
-    for (int bi = 0; bi < 3; ++bi) {
+    for (int bi = 0; bi < NB; ++bi) {
         pa[bi][0] = pack2<T>(s[bi][0][0] * i0, s[bi][0][1] * i0);
         pa[bi][1] = pack2<T>(s[bi][0][2] * i1, s[bi][0][3] * i1);
         pa[bi][2] = pack2<T>(s[bi][1][0] * i0, s[bi][1][1] * i0);
@@ -259,7 +264,7 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 #pragma unroll
-    for (int bi = 0; bi < 3; ++bi) {
+    for (int bi = 0; bi < NB; ++bi) {
         if (bi < nblk) {
             const int vrow = key_row(bi, (lane & 7) + 8 * ((lane >> 3) & 1));
             const uint32_t vb = smem_u32(Vs + (size_t)vrow * PITCH);
@@ -305,8 +310,9 @@ bool hsa_span_attn_fwd_tc128_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_v
     if (D != 64 && D != 128) return false;
     if (N < kT128 || (N & (N - 1)) != 0) return false;
     const int L = ilog2((unsigned)N);
-    if (L + 3 > 16) return false;                        // the warp's tree keys must fit one 16-key block
+    if (L + 3 > 32) return false;                        // the warp's tree keys must fit two 16-key blocks
     if (radius < 0 || radius > 16) return false;
+    if (((radius + 15) / 16 + 1) + ((L + 3 + 15) / 16) > 4) return false;
     if (B < 1 || H < 1) return false;
     if ((int64_t)(N / kT128) * H * B > 0x7fffffffLL) return false;
     if (!view_vec_ok(Q, 2) || !view_vec_ok(K, 2) || !view_vec_ok(V, 2) || !view_vec_ok(Out, 2)) return false;
@@ -317,11 +323,14 @@ template <typename T, int D>
 static int launch_tc128(const SpanTc128Args &a, int B, cudaStream_t st) {
     const size_t smem = (size_t)2 * a.kv_rows * (D * 2);
     const int64_t total = (int64_t)B * (a.N / kT128) * a.H;
-    auto kernel = span_fwd_tc128_kernel<T, D>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_fwd(tc128): shared memory %zu: %s", smem, cudaGetErrorString(e));
-    kernel<<<(unsigned)total, 256, smem, st>>>(a);
-    return launch_status("hsa_span_attn_fwd(tc128)");
+    const int nblk = (a.RB + 1) + ((a.L + 3 + 15) >> 4);
+    auto go = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_fwd(tc128): shared memory %zu: %s", smem, cudaGetErrorString(e));
+        kernel<<<(unsigned)total, 256, smem, st>>>(a);
+        return launch_status("hsa_span_attn_fwd(tc128)");
+    };
+    return nblk <= 3 ? go(span_fwd_tc128_kernel<T, D, 3>) : go(span_fwd_tc128_kernel<T, D, 4>);
 }
 
 int hsa_span_attn_fwd_tc128(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H, int D,

@@ -235,7 +235,8 @@ def test_span_attention_tensor_core(hsa, case, causal, dtype):
 
 
 @pytest.mark.parametrize("case", [(1, 128, 1, 64, 0), (2, 128, 3, 64, 5), (1, 256, 2, 128, 16), (2, 1024, 3, 64, 8),
-                                  (1, 4096, 2, 128, 16), (1, 8192, 1, 128, 7), (3, 512, 5, 128, 1)])
+                                  (1, 4096, 2, 128, 16), (1, 8192, 1, 128, 7), (3, 512, 5, 128, 1),
+                                  (1, 16384, 1, 128, 16), (1, 32768, 1, 64, 9)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_span_attention_tensor_core_128_leaf_tiles(hsa, case, dtype):
     """The 128-leaf-tile forward (algo 4, causal) against the oracle, and bit-for-bit LSE agreement is not
