@@ -206,8 +206,8 @@ def run_reference(args):
         "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * secs / max(1, args.steps), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "B": 1, "N": N, "H": H, "D": D, "radius": R, "causal": causal,
-                   "l2": "cpu run"},
+        "config": {"workload": args.workload, "B_per_gpu": B, "N": N, "H": H, "D": D, "radius": R, "causal": causal,
+                   "sharding": "rank 0 only", "l2": "cpu run on a bounded sample of the workload's leaves"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": f"{toks} leaves x {H} heads of one batch entry over {args.steps} steps "
                                    f"(eager PyTorch CPU oracle, {cores} threads)"},
