@@ -529,6 +529,25 @@ static BwdTcPlan plan_bwd_tc(int N, int D, int radius, bool causal) {
 
 using namespace hsa;
 
+// Sum of the tiles' partial rows for the nodes of level >= 6 (shared with the 8-warp kernel).
+int hsa_span_bwd_upper_reduce(float *partial, void *dk, void *dv, int64_t dk_bs, int64_t dk_rs, int64_t dv_bs, int64_t dv_rs,
+                              int B, int N, int H, int D, int causal, int dtype, cudaStream_t st) {
+    SpanBwdTcArgs a{};
+    a.partial = partial; a.dk = dk; a.dv = dv;
+    a.dk_bs = dk_bs; a.dk_rs = dk_rs; a.dv_bs = dv_bs; a.dv_rs = dv_rs;
+    a.N = N; a.L = ilog2((unsigned)N); a.H = H;
+    const int nodes = 2 * N - 1 - level_base(N, kTileLog);
+    dim3 g2((unsigned)nodes, (unsigned)H, (unsigned)B);
+    if (dtype == HSA_BF16) {
+        if (causal) span_bwd_upper_reduce_kernel<__nv_bfloat16, true><<<g2, 64, 0, st>>>(a, D);
+        else span_bwd_upper_reduce_kernel<__nv_bfloat16, false><<<g2, 64, 0, st>>>(a, D);
+    } else {
+        if (causal) span_bwd_upper_reduce_kernel<__half, true><<<g2, 64, 0, st>>>(a, D);
+        else span_bwd_upper_reduce_kernel<__half, false><<<g2, 64, 0, st>>>(a, D);
+    }
+    return launch_status("hsa_span_attn_bwd(tc, upper levels)");
+}
+
 bool hsa_span_attn_bwd_tc_supported(const hsa_view *views, int nviews, int B, int N, int H, int D, int radius,
                                     int causal, int dtype) {
     if (dtype != HSA_BF16 && dtype != HSA_F16) return false;

@@ -241,8 +241,8 @@ def test_span_attention_tensor_core(hsa, case, causal, dtype):
 def test_span_attention_tensor_core_128_leaf_tiles(hsa, case, dtype):
     """The 128-leaf-tile forward (algo 4, causal) against the oracle, and bit-for-bit LSE agreement is not
     required between tile sizes, only the common tolerance."""
-    run_span_case(hsa, *case, True, dtype, algo=4, check_grad=False)
-    run_span_case(hsa, *case, True, dtype, algo=3, check_grad=False)
+    run_span_case(hsa, *case, True, dtype, algo=4)          # 128-leaf forward and the 8-warp backward
+    run_span_case(hsa, *case, True, dtype, algo=3)          # 64-leaf forward and the 4-warp backward
 
 
 def test_tensor_core_kernel_refuses_what_it_cannot_take(hsa):
