@@ -33,6 +33,7 @@ struct SpanBwdTcArgs {
     int q_rows;         // query rows staged per tile (tile + halo)
     int persist_off;    // byte offsets into shared memory
     int kt_off, vt_off, q_off, go_off, stat_off;
+    int ds_off;         // dS^T tiles handed from the key-side phase to the query-side phase
     float scale_log2e, scale;
 };
 
@@ -40,11 +41,6 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
     uint32_t y;
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
     return y;
-}
-
-template <typename T>
-__device__ __forceinline__ void store_pair(T *p, float a, float b) {
-    *reinterpret_cast<uint32_t *>(p) = pack2<T>(a, b);
 }
 
 template <bool CAUSAL> __device__ __forceinline__ constexpr int first_partial_slot() { return CAUSAL ? 8 : 15; }
@@ -67,6 +63,9 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
     unsigned char *Gs = smem + a.go_off;                        // dOut rows
     float *lse_s = reinterpret_cast<float *>(smem + a.stat_off);
     float *dl_s = lse_s + a.q_rows;
+    // dS^T tiles [query block of the tile][relative key block][16 keys][16 queries] in T, 512 bytes each; the two
+    // 16-byte halves of a row are swapped in rows 4..7 and 12..15 so that 8-row matrix loads hit distinct banks
+    unsigned char *ds_tiles = smem + a.ds_off;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % a.H;
@@ -168,6 +167,7 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
     }
 
     const float c2 = a.scale_log2e, sc = a.scale;
+    const int nrel = CAUSAL ? RB + 1 : 2 * RB + 1;          // key blocks a query block can see = tiles per query block
 
     // ================================================================ phase B: leaf keys of the tile
     {
@@ -226,6 +226,16 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
             pa[2] = pack2<T>(p[1][0], p[1][1]); pa[3] = pack2<T>(p[1][2], p[1][3]);
             da[0] = pack2<T>(ds[0][0], ds[0][1]); da[1] = pack2<T>(ds[0][2], ds[0][3]);
             da[2] = pack2<T>(ds[1][0], ds[1][1]); da[3] = pack2<T>(ds[1][2], ds[1][3]);
+            // hand dS^T of this (key block, query block) pair to the query-side phase when the queries are the tile's own
+            const int qblk = warp + qb;
+            if (qblk >= 0 && qblk < 4) {
+                unsigned char *tile_p = ds_tiles + (size_t)(qblk * nrel + (CAUSAL ? qb : qb + RB)) * 512;
+                const int sw = ((qrow >> 2) & 1) * 16;               // same for rows qrow and qrow + 8
+                *reinterpret_cast<uint32_t *>(tile_p + qrow * 32 + (0 ^ sw) + 4 * quad) = da[0];
+                *reinterpret_cast<uint32_t *>(tile_p + (qrow + 8) * 32 + (0 ^ sw) + 4 * quad) = da[1];
+                *reinterpret_cast<uint32_t *>(tile_p + qrow * 32 + (16 ^ sw) + 4 * quad) = da[2];
+                *reinterpret_cast<uint32_t *>(tile_p + (qrow + 8) * 32 + (16 ^ sw) + 4 * quad) = da[3];
+            }
             const int trow = qr0 + (lane & 7) + 8 * ((lane >> 3) & 1);           // B rows for [queries x d]
             const uint32_t gt = smem_u32(Gs + (size_t)trow * PITCH + (lane >> 4) * 16);
             const uint32_t qt = smem_u32(Qs + (size_t)trow * PITCH + (lane >> 4) * 16);
@@ -240,16 +250,11 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
                 mma16816<T>(dk[2 * dp + 1], da, f[2], f[3]);
             }
         }
-        T *dkg = (T *)a.dk + b * a.dk_bs + hoff + 2 * quad;
-        T *dvg = (T *)a.dv + b * a.dv_bs + hoff + 2 * quad;
+        T *dkg = (T *)a.dk + b * a.dk_bs + hoff;
+        T *dvg = (T *)a.dv + b * a.dv_bs + hoff;
         const int64_t r0 = key0 + qrow, r1 = r0 + 8;
-#pragma unroll
-        for (int nt = 0; nt < D / 8; ++nt) {
-            store_pair<T>(dkg + r0 * a.dk_rs + nt * 8, dk[nt][0], dk[nt][1]);
-            store_pair<T>(dkg + r1 * a.dk_rs + nt * 8, dk[nt][2], dk[nt][3]);
-            store_pair<T>(dvg + r0 * a.dv_rs + nt * 8, dv[nt][0], dv[nt][1]);
-            store_pair<T>(dvg + r1 * a.dv_rs + nt * 8, dv[nt][2], dv[nt][3]);
-        }
+        store_acc_rows<T, D / 8>(dkg + r0 * a.dk_rs, dkg + r1 * a.dk_rs, dk, quad);
+        store_acc_rows<T, D / 8>(dvg + r0 * a.dv_rs, dvg + r1 * a.dv_rs, dv, quad);
     }
 
     // ================================================================ phase A: own leaves as queries
@@ -300,9 +305,23 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
         }
     };
 
+    __syncthreads();        // every dS^T tile of the key-side phase is in shared memory
+
     for (int bi = 0; bi < nbb; ++bi) {
         const int r0 = t0 + lw + 16 * (bi - RB);                                 // first key row of the block
         if (r0 >= N || r0 + 16 <= 0) continue;
+        const int kblk = warp + bi - RB;                                         // key block relative to the tile
+        if (kblk >= 0 && kblk < 4) {
+            // the key-side phase already formed dS for this pair: read it back transposed (queries as rows)
+            const int rel = RB - bi;                                             // query block = key block + rel
+            const unsigned char *tile_p = ds_tiles + (size_t)(warp * nrel + (CAUSAL ? rel : rel + RB)) * 512;
+            const int key = (lane & 7) + 8 * (lane >> 4);
+            const int hsel = (((lane >> 3) & 1) * 16) ^ (((key >> 2) & 1) * 16);
+            uint32_t da[4];
+            ldmatrix_x4_trans(da, smem_u32(tile_p + key * 32 + hsel));
+            dq_block(Kb, lw + 16 * bi + (lane & 7) + 8 * ((lane >> 3) & 1), da);
+            continue;
+        }
         float s[2][4], dp[2][4];
         score_block(Kb, Vb, lw + 16 * bi + (lane & 7) + 8 * (lane >> 4), s, dp);
         const bool edge = r0 < 0 || r0 + 16 > N;
@@ -381,8 +400,8 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
                 const bool ok = l <= 3 || !CAUSAL || (((t0 + lw) >> 4) & 1);
                 if (ok) {
                     const int64_t gr = level_base(N, l) + node;
-                    fin_k[hh] = (T *)a.dk + b * a.dk_bs + gr * a.dk_rs + hoff + 2 * quad;
-                    fin_v[hh] = (T *)a.dv + b * a.dv_bs + gr * a.dv_rs + hoff + 2 * quad;
+                    fin_k[hh] = (T *)a.dk + b * a.dk_bs + gr * a.dk_rs + hoff;
+                    fin_v[hh] = (T *)a.dv + b * a.dv_bs + gr * a.dv_rs + hoff;
                 }
             } else if (l >= 5) {
                 par[hh] = persist + ((size_t)(warp * nps + (slot - fps)) * 2) * D + 2 * quad;
@@ -402,14 +421,13 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
                 mma16816<T>(acc[2 * dpp], which ? pt : dt, f[0], f[1]);
                 mma16816<T>(acc[2 * dpp + 1], which ? pt : dt, f[2], f[3]);
             }
+            // rows owned by this warp alone go out as T (all lanes take part in the transpose; rows that are
+            // partial sums or unused pass a null pointer)
+            store_acc_rows<T, D / 8>(which ? fin_v[0] : fin_k[0], which ? fin_v[1] : fin_k[1], acc, quad);
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-                T *fin = which ? fin_v[hh] : fin_k[hh];
                 float *pp = par[hh] ? par[hh] + which * D : nullptr;
-                if (fin != nullptr) {
-#pragma unroll
-                    for (int nt = 0; nt < D / 8; ++nt) store_pair<T>(fin + nt * 8, acc[nt][2 * hh], acc[nt][2 * hh + 1]);
-                } else if (pp != nullptr) {
+                if (pp != nullptr) {
 #pragma unroll
                     for (int nt = 0; nt < D / 8; ++nt)
                         *reinterpret_cast<float2 *>(pp + nt * 8) = make_float2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
@@ -420,13 +438,9 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
 
     // dQ of the warp's leaves
     {
-        T *dqg = (T *)a.dq + b * a.dq_bs + hoff + 2 * quad;
+        T *dqg = (T *)a.dq + b * a.dq_bs + hoff;
         const int64_t r0 = t0 + lw + qrow, r1 = r0 + 8;
-#pragma unroll
-        for (int nt = 0; nt < D / 8; ++nt) {
-            store_pair<T>(dqg + r0 * a.dq_rs + nt * 8, dq[nt][0], dq[nt][1]);
-            store_pair<T>(dqg + r1 * a.dq_rs + nt * 8, dq[nt][2], dq[nt][3]);
-        }
+        store_acc_rows<T, D / 8>(dqg + r0 * a.dq_rs, dqg + r1 * a.dq_rs, dq, quad);
     }
     __syncthreads();
 
@@ -497,7 +511,7 @@ __global__ void span_bwd_upper_reduce_kernel(SpanBwdTcArgs a, int D) {
 
 struct BwdTcPlan {
     int RB, band_rows, tree_rows, q_rows, nup;
-    int persist_off, kt_off, vt_off, q_off, go_off, stat_off;
+    int persist_off, kt_off, vt_off, q_off, go_off, stat_off, ds_off;
     size_t smem;
 };
 
@@ -521,6 +535,8 @@ static BwdTcPlan plan_bwd_tc(int N, int D, int radius, bool causal) {
     p.q_off = (int)off; off += (size_t)p.q_rows * PITCH;
     p.go_off = (int)off; off += (size_t)p.q_rows * PITCH;
     p.stat_off = (int)off; off += (size_t)2 * p.q_rows * sizeof(float);
+    off = (off + 15) / 16 * 16;
+    p.ds_off = (int)off; off += (size_t)4 * (causal ? p.RB + 1 : 2 * p.RB + 1) * 512;
     p.smem = off;
     return p;
 }
@@ -603,7 +619,7 @@ int hsa_span_attn_bwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const
     a.N = N; a.L = ilog2((unsigned)N); a.H = H; a.R = radius < N ? radius : N; a.RB = p.RB;
     a.band_rows = p.band_rows; a.tree_rows = p.tree_rows; a.q_rows = p.q_rows;
     a.persist_off = p.persist_off; a.kt_off = p.kt_off; a.vt_off = p.vt_off; a.q_off = p.q_off; a.go_off = p.go_off;
-    a.stat_off = p.stat_off;
+    a.stat_off = p.stat_off; a.ds_off = p.ds_off;
     a.scale = 1.0f / sqrtf((float)D);
     a.scale_log2e = 1.4426950408889634f * a.scale;
     if (dtype == HSA_BF16)

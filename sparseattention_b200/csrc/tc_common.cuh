@@ -113,6 +113,43 @@ __device__ __forceinline__ BlockRef block_ref(int o, int RB, int nbb) {
     return {true, o};
 }
 
+// 4x4 transpose inside every quad of lanes.  In: w[t] = this lane's 32-bit word (two columns) of n-tile t of a
+// group of four n-tiles.  Out: lane q holds, in order, the words the four lanes had for n-tile q, i.e. eight
+// consecutive columns (16 bytes) of one n-tile.  Two butterfly rounds (lane ^ 1, lane ^ 2).
+__device__ __forceinline__ void quad_transpose4(uint32_t (&w)[4], int quad) {
+    const bool b0 = quad & 1, b1 = quad & 2;
+    uint32_t x0 = b0 ? w[0] : w[1], x1 = b0 ? w[2] : w[3];
+    x0 = __shfl_xor_sync(0xffffffffu, x0, 1);
+    x1 = __shfl_xor_sync(0xffffffffu, x1, 1);
+    if (b0) { w[0] = x0; w[2] = x1; } else { w[1] = x0; w[3] = x1; }
+    x0 = b1 ? w[0] : w[2];
+    x1 = b1 ? w[1] : w[3];
+    x0 = __shfl_xor_sync(0xffffffffu, x0, 2);
+    x1 = __shfl_xor_sync(0xffffffffu, x1, 2);
+    if (b1) { w[0] = x0; w[1] = x1; } else { w[2] = x0; w[3] = x1; }
+}
+
+// Store an accumulator block (NT n-tiles of 8 columns, rows qrow and qrow + 8 of a 16-row block) as T to two
+// global rows.  After the quad transpose every lane writes 16 contiguous bytes, so one store instruction
+// covers 64 contiguous bytes of each of 8 rows instead of 16.  row0 / row1 point at column 0 of the block.
+template <typename T, int NT>
+__device__ __forceinline__ void store_acc_rows(T *row0, T *row1, const float (&acc)[NT][4], int quad) {
+    static_assert(NT % 4 == 0, "n-tiles come in groups of four");
+#pragma unroll
+    for (int j = 0; j < NT / 4; ++j) {
+        uint32_t w0[4], w1[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            w0[t] = pack2<T>(acc[4 * j + t][0], acc[4 * j + t][1]);
+            w1[t] = pack2<T>(acc[4 * j + t][2], acc[4 * j + t][3]);
+        }
+        quad_transpose4(w0, quad);
+        quad_transpose4(w1, quad);
+        if (row0 != nullptr) *reinterpret_cast<uint4 *>(row0 + (4 * j + quad) * 8) = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+        if (row1 != nullptr) *reinterpret_cast<uint4 *>(row1 + (4 * j + quad) * 8) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+    }
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
