@@ -370,7 +370,26 @@ def run_ours(args):
         extras["parent_build_fwd_all_levels"] = {
             "ms": pms, "launches": len(sizes), "achieved_gbs": palg / (pms * 1e-3) / 1e9,
             "frac_of_hbm": palg / (pms * 1e-3) / 1e9 / peak}
-        del Pq, Pk, Pv, Ck, Cv
+        # backward of every level through the C ABI directly (15 rows per parent)
+        lib = _lib.load()
+        grads = [torch.empty_like(t) for t in (Pq, Pk, Pv, Ck, Cv)]
+        gq, gk, gv = (torch.split(t, sizes, dim=1) for t in grads[:3])
+        gout = torch.randn_like(Pq)
+        gos = torch.split(gout, sizes, dim=1)
+        dt = _lib.dtype_code(Pq)
+
+        def parents_bwd():
+            for lvl, P in enumerate(sizes):
+                views = [_lib.rows_view(t) for t in (gos[lvl], qs[lvl], ks[lvl], vs[lvl], Ck[:, :2 * P], Cv[:, :2 * P],
+                                                     gq[lvl], gk[lvl], gv[lvl], grads[3][:, :2 * P], grads[4][:, :2 * P])]
+                _lib.check(lib.hsa_parent_nodes_bwd(*views, B, P, H, D, dt, _lib.stream_ptr(device)), "hsa_parent_nodes_bwd")
+
+        pbms = time_cuda(parents_bwd, bsteps, 3, lambda: None) / bsteps
+        pbalg = B * H * D * esize * 15 * (N - 1)
+        extras["parent_build_bwd_all_levels"] = {
+            "ms": pbms, "launches": len(sizes), "achieved_gbs": pbalg / (pbms * 1e-3) / 1e9,
+            "frac_of_hbm": pbalg / (pbms * 1e-3) / 1e9 / peak}
+        del Pq, Pk, Pv, Ck, Cv, grads, gout
 
     # ---- the model that calls the layer: data-parallel LM training step (all ranks) ---------------
     if not args.no_lm:
