@@ -235,12 +235,15 @@ def run_lm(args, device, world, rank, barrier, use_dist):
     torch.manual_seed(0)
     model = TransformerLM(vocab, 512, 8, 2048, 6, dropout=0.1, window_size=16).to(device)
     avg = BucketedGradAverager(model.parameters())
-    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True)
+    use_graph = not args.no_cuda_graph
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True, capturable=use_graph)
     host_tokens = zipf_tokens(cfg["batch"], cfg["seq"] + 1, vocab, seed=4321 + rank).pin_memory()
+    tokens = torch.empty(host_tokens.shape, dtype=host_tokens.dtype, device=device)
+    loss_buf = torch.zeros((), device=device)
     losses = []
 
-    def step():
-        tokens = host_tokens.to(device, non_blocking=True)
+    def body():
+        tokens.copy_(host_tokens, non_blocking=True)        # this step's inputs come from pinned host memory
         avg.zero_grad()
         with torch.autocast("cuda", dtype=torch.bfloat16):
             loss = lm_loss(model, tokens)
@@ -248,7 +251,39 @@ def run_lm(args, device, world, rank, barrier, use_dist):
         avg.finish()
         torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
         opt.step()
-        losses.append(loss.detach())
+        loss_buf.copy_(loss.detach())
+
+    # The whole step is captured once in a CUDA graph and replayed (the launches of the ~2500 small kernels of
+    # a step otherwise cost more host time than the GPU needs); eager launching is used if capture is refused.
+    graph = None
+    if use_graph:
+        try:
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    body()
+            torch.cuda.current_stream(device).wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                body()
+        except Exception as exc:                              # pragma: no cover - depends on the runtime
+            graph = None
+            graph_error = f"{type(exc).__name__}: {exc}"[:200]
+            torch.cuda.synchronize()
+    if use_dist:                                              # every rank must take the same path
+        flag = torch.tensor([1 if graph is not None else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            graph = None
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        else:
+            body()
+        losses.append(loss_buf.clone())
 
     steps = max(3, min(args.steps, 10))
     ms = time_cuda(step, steps, 3, barrier)
@@ -263,8 +298,9 @@ def run_lm(args, device, world, rank, barrier, use_dist):
            "global_batch": cfg["batch"] * world, "seq_len": cfg["seq"], "params": nparams,
            "allreduce_bytes_per_step": avg.bytes_per_step() if world > 1 else 0,
            "loss_first": float(losses[0]), "loss_last": float(losses[-1]),
-           "step": "fwd + label-smoothed CE + bwd + NCCL grad all-reduce + clip + AdamW, bf16 autocast"}
-    del model, opt, avg
+           "step": "fwd + label-smoothed CE + bwd + NCCL grad all-reduce + clip + AdamW, bf16 autocast",
+           "cuda_graph": graph is not None}
+    del model, opt, avg, graph
     torch.cuda.empty_cache()
     return out
 
@@ -467,6 +503,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-lm", action="store_true")
+    ap.add_argument("--no-cuda-graph", action="store_true", help="launch the LM step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--lm", default="lm_8x4096", choices=sorted(LM_CONFIGS))
     ap.add_argument("--sweep", action="store_true", help="print the forward sweep over N and batch instead of the JSON line")
     args = ap.parse_args()
