@@ -12,7 +12,7 @@ from ctypes import Structure, c_char_p, c_float, c_int, c_int64, c_size_t, c_voi
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libhsa_b200.so")
+LIB_PATH = os.environ.get("HSA_B200_LIBRARY", os.path.join(HERE, "libhsa_b200.so"))   # override: a build to compare
 
 HSA_F32, HSA_BF16, HSA_F16 = 0, 1, 2
 _DTYPE_CODE = {torch.float32: HSA_F32, torch.bfloat16: HSA_BF16, torch.float16: HSA_F16}

@@ -180,76 +180,93 @@ span_bwd_tc_kernel(SpanBwdTcArgs a) {
         const uint32_t ka = smem_u32(Kb + (size_t)krow * PITCH + (lane >> 4) * 16);
         const uint32_t va = smem_u32(Vb + (size_t)krow * PITCH + (lane >> 4) * 16);
         const int key0 = t0 + lw;                                               // first own key row
-        for (int qb = (CAUSAL ? 0 : -RB); qb <= RB; ++qb) {
-            const int qr0 = qoff + lw + 16 * qb;                                 // local row of the block's first query
-            const int nq0 = key0 + 16 * qb;                                      // its leaf index
-            if (nq0 >= N || nq0 + 16 <= 0) continue;                            // block entirely outside the sequence
-            float st[2][4], dpt[2][4];
+        // NQ consecutive query blocks at once: their score-type products advance together through the head
+        // dimension (4*NQ independent accumulator chains, the K/V fragments of the own keys loaded once).
+        // Query blocks outside the sequence need no special case: their rows are zero-filled and their
+        // log-sum-exp is +inf, so every probability comes out as 0.
+        auto key_side = [&]<int NQ>(int qb0) {
+            float st[NQ][2][4], dpt[NQ][2][4];
+            uint32_t qb_addr[NQ], gb_addr[NQ];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) st[0][e] = st[1][e] = dpt[0][e] = dpt[1][e] = 0.f;
-            {
-                const int brow = qr0 + (lane & 7) + 8 * (lane >> 4);             // B-operand rows: queries
-                const uint32_t qb_addr = smem_u32(Qs + (size_t)brow * PITCH + ((lane >> 3) & 1) * 16);
-                const uint32_t gb_addr = smem_u32(Gs + (size_t)brow * PITCH + ((lane >> 3) & 1) * 16);
+            for (int j = 0; j < NQ; ++j) {
 #pragma unroll
-                for (int ks = 0; ks < KS; ++ks) {
-                    uint32_t af[4], bf[4];
-                    ldmatrix_x4(af, ka + ks * 32);
-                    ldmatrix_x4(bf, qb_addr + ks * 32);
-                    mma16816<T>(st[0], af, bf[0], bf[1]);
-                    mma16816<T>(st[1], af, bf[2], bf[3]);
-                    ldmatrix_x4(af, va + ks * 32);
-                    ldmatrix_x4(bf, gb_addr + ks * 32);
-                    mma16816<T>(dpt[0], af, bf[0], bf[1]);
-                    mma16816<T>(dpt[1], af, bf[2], bf[3]);
+                for (int e = 0; e < 4; ++e) st[j][0][e] = st[j][1][e] = dpt[j][0][e] = dpt[j][1][e] = 0.f;
+                const int brow = qoff + lw + 16 * (qb0 + j) + (lane & 7) + 8 * (lane >> 4);     // B-operand rows: queries
+                qb_addr[j] = smem_u32(Qs + (size_t)brow * PITCH + ((lane >> 3) & 1) * 16);
+                gb_addr[j] = smem_u32(Gs + (size_t)brow * PITCH + ((lane >> 3) & 1) * 16);
+            }
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t af[4], bf[4];
+                ldmatrix_x4(af, ka + ks * 32);
+#pragma unroll
+                for (int j = 0; j < NQ; ++j) {
+                    ldmatrix_x4(bf, qb_addr[j] + ks * 32);
+                    mma16816<T>(st[j][0], af, bf[0], bf[1]);
+                    mma16816<T>(st[j][1], af, bf[2], bf[3]);
+                }
+                ldmatrix_x4(af, va + ks * 32);
+#pragma unroll
+                for (int j = 0; j < NQ; ++j) {
+                    ldmatrix_x4(bf, gb_addr[j] + ks * 32);
+                    mma16816<T>(dpt[j][0], af, bf[0], bf[1]);
+                    mma16816<T>(dpt[j][1], af, bf[2], bf[3]);
                 }
             }
-            // element (nt, e): key row kr = qrow + 8*(e>>1), query column qc = nt*8 + 2*quad + (e&1)
-            float p[2][4], ds[2][4];
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+            for (int j = 0; j < NQ; ++j) {
+                const int qb = qb0 + j;
+                const int qr0 = qoff + lw + 16 * qb;                             // local row of the block's first query
+                // element (nt, e): key row kr = qrow + 8*(e>>1), query column qc = nt*8 + 2*quad + (e&1)
+                float p[2][4], ds[2][4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int qc = nt * 8 + 2 * quad + (e & 1);
-                    const int kr = qrow + 8 * (e >> 1);
-                    const int dlt = kr - qc - 16 * qb;                           // key - query
-                    const bool wv = dlt >= -R && dlt <= (CAUSAL ? 0 : R);
-                    const bool lv = qb == 0 && ((e & 1) ? (dlt == -1) : (!CAUSAL && dlt == 1));
-                    const float bias = (wv && lv) ? 1.f : ((wv || lv) ? 0.f : -INFINITY);
-                    const float l2 = lse_s[qr0 + qc];                            // +inf outside the sequence
-                    const float pe = fast_exp2(fmaf(st[nt][e], c2, bias) - l2);
-                    p[nt][e] = pe;
-                    ds[nt][e] = pe * (dpt[nt][e] - dl_s[qr0 + qc]) * sc;
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int qc = nt * 8 + 2 * quad + (e & 1);
+                        const int kr = qrow + 8 * (e >> 1);
+                        const int dlt = kr - qc - 16 * qb;                       // key - query
+                        const bool wv = dlt >= -R && dlt <= (CAUSAL ? 0 : R);
+                        const bool lv = qb == 0 && ((e & 1) ? (dlt == -1) : (!CAUSAL && dlt == 1));
+                        const float bias = (wv && lv) ? 1.f : ((wv || lv) ? 0.f : -INFINITY);
+                        const float l2 = lse_s[qr0 + qc];                        // +inf outside the sequence
+                        const float pe = fast_exp2(fmaf(st[j][nt][e], c2, bias) - l2);
+                        p[nt][e] = pe;
+                        ds[nt][e] = pe * (dpt[j][nt][e] - dl_s[qr0 + qc]) * sc;
+                    }
+                uint32_t pa[4], da[4];
+                pa[0] = pack2<T>(p[0][0], p[0][1]); pa[1] = pack2<T>(p[0][2], p[0][3]);
+                pa[2] = pack2<T>(p[1][0], p[1][1]); pa[3] = pack2<T>(p[1][2], p[1][3]);
+                da[0] = pack2<T>(ds[0][0], ds[0][1]); da[1] = pack2<T>(ds[0][2], ds[0][3]);
+                da[2] = pack2<T>(ds[1][0], ds[1][1]); da[3] = pack2<T>(ds[1][2], ds[1][3]);
+                // hand dS^T of this (key block, query block) pair to the query-side phase when the queries are the tile's own
+                const int qblk = warp + qb;
+                if (qblk >= 0 && qblk < 4) {
+                    unsigned char *tile_p = ds_tiles + (size_t)(qblk * nrel + (CAUSAL ? qb : qb + RB)) * 512;
+                    const int sw = ((qrow >> 2) & 1) * 16;               // same for rows qrow and qrow + 8
+                    *reinterpret_cast<uint32_t *>(tile_p + qrow * 32 + (0 ^ sw) + 4 * quad) = da[0];
+                    *reinterpret_cast<uint32_t *>(tile_p + (qrow + 8) * 32 + (0 ^ sw) + 4 * quad) = da[1];
+                    *reinterpret_cast<uint32_t *>(tile_p + qrow * 32 + (16 ^ sw) + 4 * quad) = da[2];
+                    *reinterpret_cast<uint32_t *>(tile_p + (qrow + 8) * 32 + (16 ^ sw) + 4 * quad) = da[3];
                 }
-            uint32_t pa[4], da[4];
-            pa[0] = pack2<T>(p[0][0], p[0][1]); pa[1] = pack2<T>(p[0][2], p[0][3]);
-            pa[2] = pack2<T>(p[1][0], p[1][1]); pa[3] = pack2<T>(p[1][2], p[1][3]);
-            da[0] = pack2<T>(ds[0][0], ds[0][1]); da[1] = pack2<T>(ds[0][2], ds[0][3]);
-            da[2] = pack2<T>(ds[1][0], ds[1][1]); da[3] = pack2<T>(ds[1][2], ds[1][3]);
-            // hand dS^T of this (key block, query block) pair to the query-side phase when the queries are the tile's own
-            const int qblk = warp + qb;
-            if (qblk >= 0 && qblk < 4) {
-                unsigned char *tile_p = ds_tiles + (size_t)(qblk * nrel + (CAUSAL ? qb : qb + RB)) * 512;
-                const int sw = ((qrow >> 2) & 1) * 16;               // same for rows qrow and qrow + 8
-                *reinterpret_cast<uint32_t *>(tile_p + qrow * 32 + (0 ^ sw) + 4 * quad) = da[0];
-                *reinterpret_cast<uint32_t *>(tile_p + (qrow + 8) * 32 + (0 ^ sw) + 4 * quad) = da[1];
-                *reinterpret_cast<uint32_t *>(tile_p + qrow * 32 + (16 ^ sw) + 4 * quad) = da[2];
-                *reinterpret_cast<uint32_t *>(tile_p + (qrow + 8) * 32 + (16 ^ sw) + 4 * quad) = da[3];
-            }
-            const int trow = qr0 + (lane & 7) + 8 * ((lane >> 3) & 1);           // B rows for [queries x d]
-            const uint32_t gt = smem_u32(Gs + (size_t)trow * PITCH + (lane >> 4) * 16);
-            const uint32_t qt = smem_u32(Qs + (size_t)trow * PITCH + (lane >> 4) * 16);
+                const int trow = qr0 + (lane & 7) + 8 * ((lane >> 3) & 1);       // B rows for [queries x d]
+                const uint32_t gt = smem_u32(Gs + (size_t)trow * PITCH + (lane >> 4) * 16);
+                const uint32_t qt = smem_u32(Qs + (size_t)trow * PITCH + (lane >> 4) * 16);
 #pragma unroll
-            for (int dp = 0; dp < D / 16; ++dp) {
-                uint32_t f[4];
-                ldmatrix_x4_trans(f, gt + dp * 32);
-                mma16816<T>(dv[2 * dp], pa, f[0], f[1]);
-                mma16816<T>(dv[2 * dp + 1], pa, f[2], f[3]);
-                ldmatrix_x4_trans(f, qt + dp * 32);
-                mma16816<T>(dk[2 * dp], da, f[0], f[1]);
-                mma16816<T>(dk[2 * dp + 1], da, f[2], f[3]);
+                for (int dp = 0; dp < D / 16; ++dp) {
+                    uint32_t f[4];
+                    ldmatrix_x4_trans(f, gt + dp * 32);
+                    mma16816<T>(dv[2 * dp], pa, f[0], f[1]);
+                    mma16816<T>(dv[2 * dp + 1], pa, f[2], f[3]);
+                    ldmatrix_x4_trans(f, qt + dp * 32);
+                    mma16816<T>(dk[2 * dp], da, f[0], f[1]);
+                    mma16816<T>(dk[2 * dp + 1], da, f[2], f[3]);
+                }
             }
-        }
+        };
+        int qb = CAUSAL ? 0 : -RB;
+        for (; qb + 1 <= RB; qb += 2) key_side.template operator()<2>(qb);
+        if (qb <= RB) key_side.template operator()<1>(qb);
         T *dkg = (T *)a.dk + b * a.dk_bs + hoff;
         T *dvg = (T *)a.dv + b * a.dv_bs + hoff;
         const int64_t r0 = key0 + qrow, r1 = r0 + 8;
