@@ -153,6 +153,21 @@ int hsa_cross_entropy_bwd(const void *logits, int64_t row_stride, const int64_t 
                           int64_t ignore_index, int dtype, void *stream);
 
 /*
+ * LayerNorm over the last dimension of [rows, d] (contiguous), forward and backward, for the LM that
+ * calls the attention layer (the reference uses nn.LayerNorm: Hierarchical_Transformer_Pretrain.py:368-372;
+ * three of them per decoder layer).  gamma / beta / statistics are float32; x, y, dy, dx are `dtype`.
+ * d must satisfy hsa_layer_norm_supported(d).  The backward needs `partial`: float32 scratch of
+ * hsa_layer_norm_bwd_ctas(rows) * 2 * d entries; weight and bias gradients are summed in a fixed order.
+ */
+int hsa_layer_norm_supported(int d);
+int hsa_layer_norm_bwd_ctas(int64_t rows);
+int hsa_layer_norm_fwd(const void *x, const float *gamma, const float *beta, void *y, float *mean,
+                       float *rstd, int64_t rows, int d, float eps, int dtype, void *stream);
+int hsa_layer_norm_bwd(const void *x, const void *dy, const float *gamma, const float *mean,
+                       const float *rstd, void *dx, float *dgamma, float *dbeta, float *partial,
+                       int64_t rows, int d, int dtype, void *stream);
+
+/*
  * Span attention backward without any workspace argument.  No counterpart in the reference
  * project: it exists for hosts that cannot allocate device memory around the call (a plugin
  * execute hook that only receives pre-bound buffers; a server whose GPU memory is fully

@@ -47,6 +47,11 @@ SIGNATURES = {
                                       c_int, c_void_p]),
     "hsa_cross_entropy_bwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int,
                                       c_int, c_float, c_int64, c_int, c_void_p]),
+    "hsa_layer_norm_supported": (c_int, [c_int]),
+    "hsa_layer_norm_bwd_ctas": (c_int, [c_int64]),
+    "hsa_layer_norm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float,
+                                   c_int, c_void_p]),
+    "hsa_layer_norm_bwd": (c_int, [c_void_p] * 9 + [c_int64, c_int, c_int, c_void_p]),
     "hsa_span_attn_bwd_static": (c_int, [V, V, V, V, c_void_p, V, V, V, V] + [c_int] * 7 + [c_void_p]),
 }
 STATIC_SCRATCH_MAX_ELEMS = 1 << 20

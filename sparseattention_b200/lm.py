@@ -10,7 +10,9 @@ measured inside the training step the reference measures.  Differences from the 
   * the causal "mask" handed to the layers is a 1-element tensor: the layer only tests it for
     `is not None` (the reference builds an N x N boolean matrix per forward for that purpose);
   * the attention class and the span initialiser are constructor arguments, so tests can run the
-    same model around the CPU oracle;
+    same model around the CPU oracle (which then also keeps nn.LayerNorm);
+  * the three LayerNorms of a decoder layer run the library's kernels (`ops.norm.LayerNorm`, same parameters):
+    nn.LayerNorm's backward was the single largest item of the training step on B200;
   * the tied embedding / output matrix is stored with its vocabulary dimension padded up to a multiple
     of 64 rows (50257 -> 50304).  The extra rows are never looked up and their logits are cut off before
     the loss, so the function computed is unchanged; the padding only lets the library GEMM of the LM
@@ -28,6 +30,7 @@ import torch.nn.functional as F
 
 from .modules.attention import HierarchicalAttention
 from .ops.loss import cross_entropy
+from .ops.norm import LayerNorm
 from .ops.topology import generate_span_input_Y
 
 
@@ -65,9 +68,10 @@ class DecoderLayer(nn.Module):
         super().__init__()
         self.self_attn = attention_cls(d_model, num_heads, dropout, window_size=window_size)
         self.feed_forward = PositionwiseFeedForward(d_model, d_ff, dropout)
-        self.norm1 = nn.LayerNorm(d_model)
-        self.norm2 = nn.LayerNorm(d_model)
-        self.norm_y = nn.LayerNorm(d_model)
+        norm_cls = LayerNorm if attention_cls is HierarchicalAttention else nn.LayerNorm
+        self.norm1 = norm_cls(d_model)
+        self.norm2 = norm_cls(d_model)
+        self.norm_y = norm_cls(d_model)
         self.dropout = nn.Dropout(dropout)
 
     def forward(self, x, y, mask=None, return_attention: bool = False):

@@ -514,3 +514,34 @@ def test_host_entry_point_matches_device_path(hsa):
         got = F.hierarchical_attention_from_host(Q, K, V, R, True, chunks=chunks)
         torch.cuda.synchronize()
         assert torch.equal(got, want.cpu())
+
+
+@pytest.mark.parametrize("shape", [(3, 128), (4, 37, 256), (2, 100, 384), (8, 513, 512), (2, 16, 768)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layer_norm_vs_torch(hsa, shape, dtype):
+    from sparseattention_b200.ops.norm import LayerNorm
+    gen = torch.Generator().manual_seed(shape[-1])
+    d = shape[-1]
+    x = (torch.randn(*shape, generator=gen) * 2 + 0.5).to(dtype)
+    dy = torch.randn(*shape, generator=gen).to(dtype)
+    ref = torch.nn.LayerNorm(d).double()
+    with torch.no_grad():
+        ref.weight.copy_(torch.randn(d, generator=gen))
+        ref.bias.copy_(torch.randn(d, generator=gen))
+    ours = LayerNorm(d)
+    ours.load_state_dict({k: v.float() for k, v in ref.state_dict().items()})
+    ours = ours.cuda()
+    xr = x.double().requires_grad_()
+    ref(xr).backward(dy.double())
+    xo = x.cuda().requires_grad_()
+    yo = ours(xo)
+    yo.backward(dy.cuda())
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert yo.dtype == dtype
+    assert rel_err(yo.detach().float().cpu(), ref(x.double()).detach()) < tol
+    assert rel_err(xo.grad.float().cpu(), xr.grad) < tol
+    assert rel_err(ours.weight.grad.cpu(), ref.weight.grad) < (1e-5 if dtype == torch.float32 else 2e-2)
+    assert rel_err(ours.bias.grad.cpu(), ref.bias.grad) < (1e-5 if dtype == torch.float32 else 2e-2)
+    # widths the kernel does not take still work (library fallback)
+    odd = LayerNorm(100).cuda()
+    assert odd(torch.randn(3, 100, device="cuda")).shape == (3, 100)
