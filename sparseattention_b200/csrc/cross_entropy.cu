@@ -47,8 +47,17 @@ cross_entropy_fwd_kernel(const T *__restrict__ logits, int64_t row_stride, const
         for (int c = threadIdx.x; c < nfull; c += kCeThreads) {
             float v[VEC];
             load_vec<T, VEC>(x + (int64_t)c * VEC, v);
+            // one rescale per 16-byte piece: VEC + 1 exponentials instead of 2 * VEC
+            float pm = v[0], px = 0.f;
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) stat_add(st, v[e]);
+            for (int e = 1; e < VEC; ++e) pm = fmaxf(pm, v[e]);
+            const float nm = fmaxf(st.m, pm);
+            float ps = 0.f;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) { ps += expf(v[e] - nm); px += v[e]; }
+            st.s = st.s * expf(st.m - nm) + ps;
+            st.m = nm;
+            st.sx += px;
         }
         for (int j = nfull * VEC + threadIdx.x; j < V; j += kCeThreads) stat_add(st, Traits<T>::to_f(x[j]));
     } else {

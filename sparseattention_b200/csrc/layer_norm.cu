@@ -137,14 +137,26 @@ layer_norm_bwd_kernel(const T *__restrict__ x, const T *__restrict__ dy, const f
     }
 }
 
-// dgamma[c] = sum over CTAs of partial[cta][0][c], dbeta likewise, in CTA order.
-__global__ void layer_norm_bwd_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dgamma,
-                                             float *__restrict__ dbeta, int nctas, int d) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= 2 * d) return;
+// dgamma[c] = sum over CTAs of partial[cta][0][c], dbeta likewise.  A block owns 32 columns; its 8 warps sum
+// interleaved slices of the CTA list (CTA w, w+8, ...) and the 8 slice sums are added in slice order: the
+// order of additions is fixed, so the result is reproducible.
+__global__ void __launch_bounds__(256)
+layer_norm_bwd_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dgamma,
+                             float *__restrict__ dbeta, int nctas, int d) {
+    __shared__ float slice[8][32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;                      // column in [0, 2d): dgamma then dbeta
     float s = 0.f;
-    for (int k = 0; k < nctas; ++k) s += partial[(int64_t)k * 2 * d + c];
-    (c < d ? dgamma : dbeta)[c % d] = s;
+    if (c < 2 * d)
+        for (int k = w; k < nctas; k += 8) s += partial[(int64_t)k * 2 * d + c];
+    slice[w][lane] = s;
+    __syncthreads();
+    if (w == 0 && c < 2 * d) {
+        float t = slice[0][lane];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) t += slice[i][lane];
+        (c < d ? dgamma : dbeta)[c % d] = t;
+    }
 }
 
 template <typename F>
@@ -165,7 +177,7 @@ static int ln_grid(int64_t rows) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms < 1) sms = 148;
     const int64_t want = (rows + kLnWarps - 1) / kLnWarps;
-    const int64_t cap = (int64_t)sms * 4;
+    const int64_t cap = (int64_t)sms * 2;
     return (int)(want < cap ? want : cap);
 }
 
@@ -208,7 +220,7 @@ extern "C" int hsa_layer_norm_bwd(const void *x, const void *dy, const float *ga
             layer_norm_bwd_kernel<T, NV><<<ctas, kLnWarps * 32, 0, (cudaStream_t)stream>>>(
                 (const T *)x, (const T *)dy, gamma, mean, rstd, (T *)dx, partial, rows);
             if ((rc = launch_status("hsa_layer_norm_bwd"))) return;
-            layer_norm_bwd_reduce_kernel<<<(2 * d + 255) / 256, 256, 0, (cudaStream_t)stream>>>(partial, dgamma, dbeta, ctas, d);
+            layer_norm_bwd_reduce_kernel<<<(2 * d + 31) / 32, 256, 0, (cudaStream_t)stream>>>(partial, dgamma, dbeta, ctas, d);
             rc = launch_status("hsa_layer_norm_bwd(reduce)");
         });
         if (!ok) return fail(HSA_ERR_ARG, "hsa_layer_norm_bwd: width %d not supported (128, 256, 384, 512, 768)", d);
