@@ -214,7 +214,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 LM_CONFIGS = {
@@ -460,7 +460,7 @@ def run_ours(args):
             "clocks": clk.summary(),
             "extras": extras,
         }
-        print(json.dumps(line))
+        emit(line)
     if use_dist:
         dist.barrier()
         dist.destroy_process_group()
@@ -492,6 +492,15 @@ def run_sweep(args):
             del Q, K, V
 
 
+_JSON_OUT = None
+
+
+def emit(line: dict) -> None:
+    out = _JSON_OUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -510,6 +519,12 @@ def main():
     if args.sweep:
         run_sweep(args)
         return
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1; keep the real stdout for the
+    # single JSON line and send everything else to stderr.
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

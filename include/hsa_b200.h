@@ -111,7 +111,8 @@ int hsa_parent_nodes_bwd(hsa_view dOut, hsa_view Qp, hsa_view Kp, hsa_view Vp, h
  *   `algo`: 0 = automatic, 1 = portable CUDA-core kernel, 2 = tensor-core kernel (bf16/f16,
  *   D in {64,128}, N >= 64 only; HSA_ERR_ARG otherwise), 3 / 4 = tensor-core kernel with
  *   64-leaf / 128-leaf tiles (4: causal, radius <= 16, N >= 128 only).  In the backward
- *   2 and 3 select the 4-warp tensor-core kernel, 4 the 8-warp variant where it applies.
+ *   2 and 3 select the 4-warp tensor-core kernel; 0 and 4 prefer the 8-warp task-parallel
+ *   kernel (causal, radius <= 16) and fall back to the 4-warp one.
  */
 int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N,
                       int H, int D, int radius, int causal, int dtype, int algo, void *stream);

@@ -106,9 +106,9 @@ extern "C" int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Ou
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
         return fail(HSA_ERR_ALIGN, "hsa_span_attn_bwd: workspace must be 256-byte aligned");
     const hsa_view views[] = {Q, K, V, Out, dOut, dQ, dK, dV};
-    // 4 asks for the 8-warp tensor-core kernel (same speed as the 4-warp one today: twice the warps, but 43 % more
-    // instructions); every other choice uses the 4-warp kernel
-    if (algo == 4 && hsa_span_attn_bwd_tc8_supported(views, 8, B, N, H, D, radius, causal, dtype))
+    // The 8-warp task-parallel kernel (causal, window radius <= 16) is preferred where it applies; 3 forces the
+    // 4-warp kernel, which also takes the non-causal case and wider windows.
+    if ((algo == 0 || algo == 4) && hsa_span_attn_bwd_tc8_supported(views, 8, B, N, H, D, radius, causal, dtype))
         return hsa_span_attn_bwd_tc8(Q, K, V, Out, LSE, dOut, dQ, dK, dV, workspace, B, N, H, D, radius, causal, dtype,
                                      (cudaStream_t)stream);
     if (algo >= 2 || (algo == 0 && hsa_span_attn_bwd_tc_supported(views, 8, B, N, H, D, radius, causal, dtype)))
