@@ -223,14 +223,17 @@ LM_CONFIGS = {
 }
 
 
-def run_lm(args, device, world, rank, barrier, use_dist):
+def run_lm(args, device, world, rank, barrier, use_dist, strong=False):
     """Training step (forward, loss, backward, gradient all-reduce, clip, AdamW) of the hierarchical LM
-    on Zipf(1.1) token ids; per-GPU batch fixed (weak scaling).  Returns whole-job tokens/s."""
+    on Zipf(1.1) token ids.  Per-GPU batch fixed (weak scaling) unless `strong`, which splits the config's
+    batch over the ranks (global batch fixed).  Returns whole-job tokens/s."""
     import torch.distributed as dist
     from sparseattention_b200.dp import BucketedGradAverager
     from sparseattention_b200.lm import TransformerLM, lm_loss, zipf_tokens
 
-    cfg = LM_CONFIGS[args.lm]
+    cfg = dict(LM_CONFIGS[args.lm])
+    if strong:
+        cfg["batch"] //= world
     vocab = 50257
     torch.manual_seed(0)
     model = TransformerLM(vocab, 512, 8, 2048, 6, dropout=0.1, window_size=16).to(device)
@@ -294,7 +297,8 @@ def run_lm(args, device, world, rank, barrier, use_dist):
     ms /= steps
     tok = cfg["batch"] * cfg["seq"] * world
     nparams = sum(p.numel() for p in model.parameters())
-    out = {"config": args.lm, "tokens_per_s": tok / (ms * 1e-3), "ms_per_step": ms, "steps": steps,
+    out = {"config": args.lm, "scaling": "strong" if strong else "weak", "tokens_per_s": tok / (ms * 1e-3),
+           "ms_per_step": ms, "steps": steps,
            "global_batch": cfg["batch"] * world, "seq_len": cfg["seq"], "params": nparams,
            "allreduce_bytes_per_step": avg.bytes_per_step() if world > 1 else 0,
            "loss_first": float(losses[0]), "loss_last": float(losses[-1]),
@@ -430,6 +434,9 @@ def run_ours(args):
     # ---- the model that calls the layer: data-parallel LM training step (all ranks) ---------------
     if not args.no_lm:
         extras["lm_train"] = run_lm(args, device, world, rank, barrier, use_dist)
+        if world > 1 and LM_CONFIGS[args.lm]["batch"] % world == 0:
+            # secondary line: the same global batch as one GPU, split over the ranks
+            extras["lm_train_strong"] = run_lm(args, device, world, rank, barrier, use_dist, strong=True)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -42,6 +42,27 @@ __device__ __forceinline__ uint32_t piece_off(int piece_even, int x) {
     return (uint32_t)((((piece_even & 7) ^ x) | (piece_even & 8)) * 16);
 }
 
+// Tree rows in shared memory: rows 8*qb .. 8*qb+7 hold what query block qb alone attends to (slots 0..7: four
+// even level-1 nodes, two even level-2 nodes, one level-3 node, the level-4 sibling of the block), row 32 the
+// tile's left level-5 node, rows 33.. one node per level >= 6.  Any 8 consecutive slots of a block thus sit in 8
+// consecutive rows, which the swizzle spreads over all banks.
+constexpr int kTreeIn8 = 33;
+// Tree key slot s of query block qb -> level (or -1 past the last level) and shared-memory row; jj = node index
+// relative to the first node of that level below the block.
+__device__ __forceinline__ int tree_slot8(int s, int qb, int L, int &row, int &jj) {
+    jj = 0;
+    if (s < 8) {
+        row = 8 * qb + s;
+        if (s < 4) { jj = 2 * s; return 1; }
+        if (s < 6) { jj = 2 * (s - 4); return 2; }
+        return s == 6 ? 3 : 4;
+    }
+    const int l = s - 3;
+    if (l >= L) { row = 0; return -1; }
+    row = 32 + (s - 8);
+    return l;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(256, 2)
 span_bwd_tc8_kernel(SpanBwd8Args a) {
@@ -51,8 +72,8 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
     constexpr int KS = D / 16;
     constexpr int CW = D / 2;              // columns of the head dimension per output task
     constexpr int NTH = CW / 8;            // its 8-column n-tiles
-    constexpr int TIN = 31;                // in-tile tree rows (left children of levels 1..5)
     constexpr int FPS = 8;                 // first tree slot that is a partial sum (level 5)
+    constexpr int PR = 2 * D + 8;          // floats per partial row (dK | dV), padded: 8 rows written at once spread over the banks
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char *Vb = smem;
     unsigned char *Kb = smem + a.kb_off;
@@ -66,7 +87,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
     // 12..15 so that 8-row matrix loads hit distinct banks
     unsigned char *tiles = smem + a.tiles_off;       // (kb, rel): P^T at ((kb*2+rel)*2), dS^T at +1; halo pair dS^T at 16
     unsigned char *ttiles = smem + a.ttiles_off;     // (qb, tb): P at ((qb*ntb+tb)*2), dS at +1   (inside the dead V band)
-    float *persist = reinterpret_cast<float *>(smem + a.persist_off);   // [qb][1+nup][2][D], inside dead bands
+    float *persist = reinterpret_cast<float *>(smem + a.persist_off);   // [qb][1+nup] rows of PR floats, inside dead bands
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ntiles = a.N / kTile;
@@ -98,19 +119,23 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
             const T *gc = (const T *)base + b * bs + hoff + c * 8;
             uint32_t dst = smem_u32(S) + rg * PITCH + pc;
             for (int f = rg; f < a.tree_rows; f += RPI, dst += RPI * PITCH) {
-                int rr;
+                int l, node;
                 bool ok = true;
-                if (f < TIN) {
-                    const int rem = 32 - f;
-                    const int l = 5 - (31 - __clz(rem - 1));
-                    const int i = f - tree_level_off<true>(l);
-                    rr = level_base(N, l) + (t0 >> l) + 2 * i;
+                if (f < 32) {
+                    const int qb = f >> 3, sl = f & 7;
+                    if (sl < 4) { l = 1; node = 8 * qb + 2 * sl; }
+                    else if (sl < 6) { l = 2; node = 4 * qb + 2 * (sl - 4); }
+                    else if (sl == 6) { l = 3; node = 2 * qb; }
+                    else { l = 4; node = qb ^ 1; ok = qb & 1; }          // the left sibling exists for odd blocks only
+                    node += t0 >> l;
+                } else if (f == 32) {
+                    l = 5; node = t0 >> 5;
                 } else {
-                    const int l = kTileLog + (f - TIN);
+                    l = kTileLog + (f - kTreeIn8);
                     ok = (t0 >> l) & 1;
-                    rr = level_base(N, l) + ((t0 >> l) ^ 1);
+                    node = (t0 >> l) ^ 1;
                 }
-                cp_async16(dst, gc + (int64_t)rr * rs, ok);
+                cp_async16(dst, gc + (int64_t)(level_base(N, l) + node) * rs, ok);
             }
         };
         stage_rows(a.go, a.go_bs, a.go_rs, Gs, t0);
@@ -124,8 +149,8 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
         cp_async_commit();
 
         // Pull the leaf rows of the tile that a later CTA will work on into L2, so that its staging pays L2 latency
-        // instead of DRAM latency.  CTAs are handed out in blockIdx order and two are resident per SM: pf_dist =
-        // one CTA per SM ahead measured best (further ahead the lines are evicted again before they are used).
+        // instead of DRAM latency.  CTAs are handed out in blockIdx order and two are resident per SM: three
+        // quarters of the SM count ahead measured best (further ahead, lines are evicted again before their use).
         {
             const int64_t nb = (int64_t)blockIdx.x + a.pf_dist;
             if (nb < (int64_t)gridDim.x) {
@@ -144,6 +169,15 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
                         case 3: src = (const T *)a.v + b2 * a.v_bs + row * a.v_rs; break;
                         default: src = (const T *)a.out + b2 * a.o_bs + row * a.o_rs; break;
                     }
+                    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(src + (int64_t)h2 * D + (rem % LPR) * 64));
+                }
+                // ... and the left children of levels 1..5 inside that tile (31 rows of K and of V)
+                for (int i = tid; i < 2 * 31 * LPR; i += 256) {
+                    const int which = i / (31 * LPR), rem = i % (31 * LPR);
+                    const int f = rem / LPR;
+                    const int l = 5 - (31 - __clz(31 - f));                 // 16, 8, 4, 2, 1 nodes of levels 1..5
+                    const int64_t row = level_base(N, l) + ((tile2 * kTile) >> l) + 2 * (f - (32 - (64 >> l)));
+                    const T *src = which ? (const T *)a.v + b2 * a.v_bs + row * a.v_rs : (const T *)a.k + b2 * a.k_bs + row * a.k_rs;
                     asm volatile("prefetch.global.L2 [%0];\n" ::"l"(src + (int64_t)h2 * D + (rem % LPR) * 64));
                 }
             }
@@ -277,7 +311,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
     // Score task of tree block tb of query block qb: P and dS with the 16 queries as rows, the 16 slots as columns.
     auto tree_pair = [&](int qb, int tb) {
         int rowA, jj;
-        tree_slot<true>(16 * tb + (lane & 7) + 8 * (lane >> 4), qb, L, rowA, jj);
+        tree_slot8(16 * tb + (lane & 7) + 8 * (lane >> 4), qb, L, rowA, jj);
         float s[2][4], dp[2][4];
         product2(Qs, Gs, 16 * qb + (lane & 7) + 8 * ((lane >> 3) & 1), Kt, Vt, rowA, s, dp);
         const float lse0 = lse_s[16 * qb + qrow], lse1 = lse_s[16 * qb + qrow + 8];
@@ -290,7 +324,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
                 const int slot = 16 * tb + nt * 8 + 2 * quad + (e & 1);
                 const int i = qrow + 8 * (e >> 1);
                 int row2, j2;
-                const int l = tree_slot<true>(slot, qb, L, row2, j2);
+                const int l = tree_slot8(slot, qb, L, row2, j2);
                 bool ok = false;
                 if (l >= 1 && l <= 3) ok = (i >> l) == j2 + 1;
                 else if (l >= 4) ok = ((t0 + 16 * qb) >> l) & 1;
@@ -341,7 +375,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
         accum_cols(acc, af, Kb, 16 * (qb + 1) + lrow, pb);
         for (int tb = 0; tb < ntb; ++tb) {
             int rowB, jj;
-            tree_slot<true>(16 * tb + lrow, qb, L, rowB, jj);
+            tree_slot8(16 * tb + lrow, qb, L, rowB, jj);
             tile_load(ttiles + (size_t)((qb * ntb + tb) * 2 + 1) * 512, af);
             accum_cols(acc, af, Kt, rowB, pb);
         }
@@ -368,7 +402,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
         for (int hh = 0; hh < 2; ++hh) {
             const int slot = 16 * tb + qrow + 8 * hh;
             int row2, j2;
-            const int l = tree_slot<true>(slot, qb, L, row2, j2);
+            const int l = tree_slot8(slot, qb, L, row2, j2);
             if (l >= 1 && l <= 4) {
                 const int node = (l <= 3) ? ((q0 >> l) + j2) : ((q0 >> 4) ^ 1);
                 if (l <= 3 || ((q0 >> 4) & 1)) {
@@ -376,7 +410,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
                     fin[hh] = (which ? (T *)a.dv + b * a.dv_bs + gr * a.dv_rs : (T *)a.dk + b * a.dk_bs + gr * a.dk_rs) + hoff + ch * CW;
                 }
             } else if (l >= 5) {
-                par[hh] = persist + ((size_t)(qb * nps + (slot - FPS)) * 2 + which) * D + ch * CW + 2 * quad;
+                par[hh] = persist + (size_t)(qb * nps + (slot - FPS)) * PR + which * D + ch * CW + 2 * quad;
             }
         }
         store_acc_rows<T, NTH>(fin[0], fin[1], acc, quad);   // all lanes take part in the transpose; null rows are skipped
@@ -420,7 +454,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
     // level 5: node 0 of the tile collects from the two query blocks under its sibling (node 1 is never attended)
     for (int idx = tid; idx < 2 * D; idx += 256) {
         const int which = idx / D, col = idx % D;
-        const float sum = persist[((size_t)(2 * nps) * 2 + which) * D + col] + persist[((size_t)(3 * nps) * 2 + which) * D + col];
+        const float sum = persist[(size_t)(2 * nps) * PR + idx] + persist[(size_t)(3 * nps) * PR + idx];
         const int64_t gr = level_base(N, 5) + (t0 >> 5);
         T *dst = which ? (T *)a.dv + b * a.dv_bs + gr * a.dv_rs + hoff : (T *)a.dk + b * a.dk_bs + gr * a.dk_rs + hoff;
         dst[col] = Traits<T>::from_f(sum);
@@ -432,7 +466,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
         if (((t0 >> l) & 1) == 0) continue;
         float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) sum += persist[((size_t)(w * nps + 1 + u) * 2) * D + rem];
+        for (int w = 0; w < 4; ++w) sum += persist[(size_t)(w * nps + 1 + u) * PR + rem];
         a.partial[((((size_t)b * a.H + h) * ntiles + tile) * nup + u) * 2 * D + rem] = sum;
     }
     // rows nobody attends to inside the tile: the right children of levels 1..5
@@ -464,7 +498,7 @@ static Bwd8Plan plan_bwd8(int N, int D) {
     const int L = ilog2((unsigned)N);
     p.nup = L - kTileLog;
     p.ntb = (3 + L + 15) / 16;
-    p.tree_rows = 31 + p.nup;
+    p.tree_rows = kTreeIn8 + p.nup;
     size_t off = 0;                                            // V band first: most of it is free after the first phase
     off += (size_t)kBand8 * PITCH;
     p.kb_off = (int)off; off += (size_t)kBand8 * PITCH;
@@ -481,7 +515,7 @@ static Bwd8Plan plan_bwd8(int N, int D) {
     // tree tiles and the partial slots reuse the V band behind its first 16 rows (and what follows it)
     p.ttiles_off = 16 * PITCH;
     p.persist_off = p.ttiles_off + p.ntb * 8 * 512;
-    const size_t persist = (size_t)4 * (1 + p.nup) * 2 * D * sizeof(float);
+    const size_t persist = (size_t)4 * (1 + p.nup) * (2 * D + 8) * sizeof(float);
     p.fits = p.ntb <= 2 && (size_t)p.ttiles_off + (size_t)p.ntb * 8 * 512 <= (size_t)kBand8 * PITCH &&
              (size_t)p.persist_off + persist <= alias_end;
     return p;
@@ -540,7 +574,7 @@ int hsa_span_attn_bwd_tc8(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, cons
         int dev = 0, sms = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        a.pf_dist = sms > 0 ? sms : 148;
+        a.pf_dist = (sms > 0 ? sms : 148) * 3 / 4;
     }
     a.kb_off = p.kb_off; a.vt_off = p.vt_off; a.kt_off = p.kt_off; a.q_off = p.q_off; a.go_off = p.go_off;
     a.stat_off = p.stat_off; a.tiles_off = p.tiles_off; a.ttiles_off = p.ttiles_off; a.persist_off = p.persist_off;

@@ -282,6 +282,15 @@ def test_span_attention_config2_bf16_forward_backward(hsa):
     run_span_case(hsa, 16, 512, 8, 64, 8, True, torch.bfloat16, algo=0, seed=2)
 
 
+@pytest.mark.parametrize("case", [(1, 64, 1, 64, 16), (2, 64, 3, 128, 3), (1, 128, 2, 128, 16), (2, 2048, 2, 64, 0),
+                                  (1, 16384, 2, 64, 16), (1, 32768, 1, 128, 11)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_span_attention_automatic_choice_causal(hsa, case, dtype):
+    """algo 0 on causal half-precision inputs with a window of at most 16: the backward runs the 8-warp
+    task-parallel kernel (single-tile tree N=64, one and two tree blocks per query block)."""
+    run_span_case(hsa, *case, True, dtype, algo=0)
+
+
 def test_span_attention_full_size_properties(hsa):
     """BASELINE config 5 shape (N=4096, H16, Dh128, bf16): size-independent properties.
 
