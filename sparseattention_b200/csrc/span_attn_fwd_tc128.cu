@@ -72,20 +72,6 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
     const int quad = lane & 3, qrow = lane >> 2;
     const int n0 = t0 + lw + qrow, n1 = n0 + 8;
 
-    // ---------------------------------------------------------------- Q: global -> A-operand registers
-    uint32_t qf[KS][4];
-    {
-        const T *q0 = (const T *)a.q + b * a.q_bs + hoff + (int64_t)n0 * a.q_rs + 2 * quad;
-        const T *q1 = q0 + 8 * a.q_rs;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            qf[ks][0] = ldg32(q0 + ks * 16);
-            qf[ks][1] = ldg32(q1 + ks * 16);
-            qf[ks][2] = ldg32(q0 + ks * 16 + 8);
-            qf[ks][3] = ldg32(q1 + ks * 16 + 8);
-        }
-    }
-
     // ---------------------------------------------------------------- stage K (group 0) and V (group 1)
     {
         const int c = tid % CPR, rg = tid / CPR;        // RPI is a multiple of 8: (row & 7) == (rg & 7) on every pass
@@ -120,6 +106,21 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
         cp_async_commit();
         stage_kv(a.v, a.v_bs, a.v_rs, Vs);
         cp_async_commit();
+    }
+
+    // ---------------------------------------------------------------- Q: global -> A-operand registers
+    // (after the K/V copies: their latency runs while these 4-byte loads go through the load/store pipe)
+    uint32_t qf[KS][4];
+    {
+        const T *q0 = (const T *)a.q + b * a.q_bs + hoff + (int64_t)n0 * a.q_rs + 2 * quad;
+        const T *q1 = q0 + 8 * a.q_rs;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = ldg32(q0 + ks * 16);
+            qf[ks][1] = ldg32(q1 + ks * 16);
+            qf[ks][2] = ldg32(q0 + ks * 16 + 8);
+            qf[ks][3] = ldg32(q1 + ks * 16 + 8);
+        }
     }
 
     const int nbb = RB + 1;                 // band blocks: [the warp's own 16 leaves] (+ the 16 before them)
