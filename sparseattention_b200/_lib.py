@@ -41,6 +41,7 @@ SIGNATURES = {
     "hsa_parent_nodes_fwd": (c_int, [V, V, V, V, V, V, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "hsa_parent_nodes_bwd": (c_int, [V] * 11 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "hsa_span_attn_fwd": (c_int, [V, V, V, V, c_void_p] + [c_int] * 8 + [c_void_p]),
+    "hsa_span_attn_fwd_wait_expired": (c_int, [c_void_p]),
     "hsa_span_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 8),
     "hsa_span_attn_bwd": (c_int, [V, V, V, V, c_void_p, V, V, V, V, c_void_p, c_size_t] + [c_int] * 8 + [c_void_p]),
     "hsa_cross_entropy_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_int64,

@@ -1,14 +1,22 @@
 // Span attention forward, tensor cores, 128-leaf tiles: the variant for the common causal case
 // (radius <= 16, bf16 / f16, head dim 64 or 128, N >= 128).
 //
-// Same algorithm as span_attn_fwd_tc.cu, but a CTA covers 128 leaves with 8 warps and keeps its K/V rows
-// at an unpadded pitch of 2*D bytes with the 16-byte pieces XOR-swizzled by the row (so ldmatrix stays
-// conflict free without the padding).  What that buys: 108.5 KB of staging per CTA, two CTAs = 217 KB of
-// the SM's shared memory acting as load buffers (the forward is bound by bytes in flight), 16 warps per SM
-// instead of 12, and half the halo rows per leaf.  To stay under 128 registers per thread (two CTAs of 256
+// Same algorithm as span_attn_fwd_tc.cu, but a CTA covers 128 leaves with 8 warps and its K/V rows are
+// brought in by TMA (cp.async.bulk.tensor through tensor maps, completion on an mbarrier) instead of
+// per-thread cp.async: with no compute at all the per-thread copies top out at 5.4 TB/s on this access
+// pattern (the load/store pipe is the limiter), bulk copies reach 6.3 TB/s.  A tile needs L boxes per
+// tensor and 128-byte half of the head dim: the leaf band, the left children of levels 1..5 (a second
+// tensor map over the even rows makes each level one box), the level-6 node and one node per upper level.
+// Rows land in [half][row][128 B] planes with the hardware's 128-byte swizzle, so ldmatrix is conflict
+// free without padding.  What the tile shape buys: 108.5 KB of staging per CTA, two CTAs = 217 KB of the
+// SM's shared memory acting as load buffers, 16 warps per SM instead of 12, half the halo rows per leaf.  To stay under 128 registers per thread (two CTAs of 256
 // threads) the kernel scores all of a warp's key blocks first (at most two band blocks plus one tree block,
 // or two tree blocks once N > 8192), runs one softmax without rescaling, and normalises the probabilities
 // before P.V so the accumulators are final: the Q fragments are dead before the output accumulators live.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "tc_common.cuh"
 
 namespace hsa {
@@ -22,13 +30,36 @@ struct SpanTc128Args {
     int RB;          // ceil(R / 16): 0 or 1
     int band_rows;   // 128 + 16 * RB
     int kv_rows;     // band + 63 in-tile tree rows + (L - 7) upper rows
+    int plane_bytes; // one [rows][128 B] plane (rows padded to a multiple of 8)
     float scale_log2e;
 };
 
 constexpr int kT128 = 128, kT128Log = 7, kT128In = 63;     // causal: even nodes of levels 1..6
 
-// 16-byte piece c of shared-memory row `row` sits at piece swz(row, c)
+// Tensor maps of one tensor (K or V), all over [B, rows, H, D] with a box of 64 elements of one head:
+// band: every row, box of band_rows rows; even[l-1]: every second row, box of 64 >> l rows (level l = 1..5);
+// one: every row, box of one row.
+struct SpanTc128Maps {
+    CUtensorMap band, even[5], one;
+};
+
+// Output rows parked in shared memory before the store: 16-byte piece c of row `row` sits at piece swz(row, c)
 __device__ __forceinline__ int swz(int row, int c) { return (c & ~7) | ((c ^ row) & 7); }
+
+// CTAs whose wait for their bulk copies ran out (never expected; read by hsa_span_attn_fwd_wait_expired)
+__device__ unsigned int g_fwd128_wait_expired = 0;
+
+// Wait for phase 0 of an mbarrier, giving up after about a second.  Returns false when it gave up.
+__device__ __forceinline__ bool mbar_wait0(uint32_t mb) {
+    uint32_t done = 0;
+    const long long start = clock64();
+    while (true) {
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done) : "r"(mb), "r"(0) : "memory");
+        if (done) return true;
+        if (clock64() - start > 2000000000LL) return false;
+    }
+}
 
 // Tree key slot s of warp w (causal, 128-leaf tile) -> level and row inside the tile's tree storage.
 // Levels 1..3: the even nodes below the warp's 16 leaves (slots 0..6); then one node per level 4.. : the
@@ -51,14 +82,18 @@ __device__ __forceinline__ int tree_slot128(int s, int w, int L, int &row, int &
 
 template <typename T, int D, int NB>      // NB: key blocks per warp the code is unrolled for (3 or 4)
 __global__ void __launch_bounds__(256, 2)
-span_fwd_tc128_kernel(SpanTc128Args a) {
+span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Maps kmaps,
+                      const __grid_constant__ SpanTc128Maps vmaps) {
     constexpr int PITCH = D * 2;
     constexpr int CPR = D / 8;
-    constexpr int RPI = 256 / CPR;
     constexpr int KS = D / 16;
-    extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char *Ks = smem;
-    unsigned char *Vs = Ks + (size_t)a.kv_rows * PITCH;
+    constexpr int NH = D / 64;                      // 128-byte halves of a row
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // planes start on 1024-byte boundaries: the hardware swizzle XORs address bits 4..6 with bits 7..9
+    unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char *Ks = smem;                                        // [NH][rows][128 B]
+    unsigned char *Vs = Ks + (size_t)NH * a.plane_bytes;
+    unsigned long long *mbar = reinterpret_cast<unsigned long long *>(Vs + (size_t)NH * a.plane_bytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ntiles = a.N / kT128;
@@ -72,44 +107,44 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
     const int quad = lane & 3, qrow = lane >> 2;
     const int n0 = t0 + lw + qrow, n1 = n0 + 8;
 
-    // ---------------------------------------------------------------- stage K (group 0) and V (group 1)
-    {
-        const int c = tid % CPR, rg = tid / CPR;        // RPI is a multiple of 8: (row & 7) == (rg & 7) on every pass
-        const int pc = swz(rg, c);
-        const int ntree = kT128In + (L - kT128Log);
-        auto stage_kv = [&](const void *base, int64_t bs, int64_t rs, unsigned char *S) {
-            const T *gc = (const T *)base + b * bs + hoff + c * 8;
-            uint32_t dst = smem_u32(S) + rg * PITCH + pc * 16;
-            int r = t0 - 16 * RB + rg;
-            for (int i = rg; i < a.band_rows; i += RPI, r += RPI, dst += RPI * PITCH) {
-                const bool ok = r >= 0;                  // the band never runs past the last leaf
-                cp_async16(dst, gc + (int64_t)(ok ? r : 0) * rs, ok);
-            }
-            dst = smem_u32(S) + (a.band_rows + rg) * PITCH + pc * 16;      // band_rows is a multiple of 16
-            for (int f = rg; f < ntree; f += RPI, dst += RPI * PITCH) {
-                int rr;
-                bool ok = true;
-                if (f < kT128In) {
-                    const int rem = kT128 / 2 - f;
-                    const int l = (kT128Log - 1) - (31 - __clz(rem - 1));
-                    const int i = f - (kT128 / 2 - (kT128 >> l));
-                    rr = level_base(N, l) + (t0 >> l) + 2 * i;
-                } else {
-                    const int l = kT128Log + (f - kT128In);
-                    ok = (t0 >> l) & 1;
-                    rr = level_base(N, l) + ((t0 >> l) ^ 1);
-                }
-                cp_async16(dst, gc + (int64_t)rr * rs, ok);
-            }
-        };
-        stage_kv(a.k, a.k_bs, a.k_rs, Ks);
-        cp_async_commit();
-        stage_kv(a.v, a.v_bs, a.v_rs, Vs);
-        cp_async_commit();
+    // ---------------------------------------------------------------- stage K (barrier 0) and V (barrier 1)
+    // Thread 0 announces the bytes of all boxes; threads 0 .. 2*NH*L-1 issue one box each.  Rows nobody may
+    // attend to are loaded all the same (upper levels on the causal side) or zero-filled by the copy engine
+    // (before the first leaf), so masked scores and 0 * V products stay finite.
+    const uint32_t mbK = smem_u32(&mbar[0]), mbV = smem_u32(&mbar[1]);
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbK), "r"(1) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbV), "r"(1) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t bytes = (uint32_t)a.kv_rows * 128u * NH;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbK), "r"(bytes) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV), "r"(bytes) : "memory");
+    }
+    if (tid < 2 * NH * L) {
+        const int isv = tid / (NH * L), rem = tid % (NH * L);       // K boxes first
+        const int hf = rem / L, j = rem % L;
+        const SpanTc128Maps &maps = isv ? vmaps : kmaps;
+        const CUtensorMap *map;
+        int row, dst_row;
+        if (j == 0) {                                              // the leaf band
+            map = &maps.band; row = t0 - 16 * RB; dst_row = 0;
+        } else if (j <= 5) {                                       // left children of level j: one box over the even rows
+            map = &maps.even[j - 1]; row = (level_base(N, j) + (t0 >> j)) >> 1; dst_row = a.band_rows + (kT128 / 2 - (kT128 >> j));
+        } else if (j == 6) {                                       // the tile's left level-6 node
+            map = &maps.one; row = level_base(N, 6) + (t0 >> 6); dst_row = a.band_rows + kT128In - 1;
+        } else {                                                   // the sibling of the tile's ancestor at level j
+            map = &maps.one; row = level_base(N, j) + ((t0 >> j) ^ 1); dst_row = a.band_rows + kT128In + (j - kT128Log);
+        }
+        const uint32_t dst = smem_u32((isv ? Vs : Ks) + (size_t)hf * a.plane_bytes + (size_t)dst_row * 128);
+        asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+                     ::"r"(dst), "l"(map), "r"(64 * hf), "r"(h), "r"(row), "r"(b), "r"(isv ? mbV : mbK) : "memory");
     }
 
     // ---------------------------------------------------------------- Q: global -> A-operand registers
-    // (after the K/V copies: their latency runs while these 4-byte loads go through the load/store pipe)
+    // (after the K/V copies have been handed to the copy engine)
     uint32_t qf[KS][4];
     {
         const T *q0 = (const T *)a.q + b * a.q_bs + hoff + (int64_t)n0 * a.q_rs + 2 * quad;
@@ -155,8 +190,11 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
         return a.band_rows + row;
     };
 
-    cp_async_wait<1>();
-    __syncthreads();
+    if (!__syncthreads_and(mbar_wait0(mbK))) {        // K has landed (the wait is not expected to give up)
+        if (tid == 0) atomicAdd(&g_fwd128_wait_expired, 1u);
+        mbar_wait0(mbV);                              // a second bounded chance for this CTA's copies to finish
+        return;
+    }
 
     // ---------------------------------------------------------------- scores: NB blocks x 2 n-tiles advance together
     const float c2 = a.scale_log2e;
@@ -169,7 +207,7 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[bi][0][e] = s[bi][1][e] = 0.f;
             const int krow = key_row(min(bi, nblk - 1), (lane & 7) + 8 * (lane >> 4));
-            kb[bi] = smem_u32(Ks + (size_t)krow * PITCH);
+            kb[bi] = smem_u32(Ks + (size_t)krow * 128);
             ksw[bi] = (((lane >> 3) & 1) ^ krow) & 7;        // piece parity of this lane folded into the row's swizzle
         }
 #pragma unroll
@@ -177,7 +215,7 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
 #pragma unroll
             for (int bi = 0; bi < NB; ++bi) {
                 uint32_t kf[4];
-                ldmatrix_x4(kf, kb[bi] + ((((2 * ks) & 7) ^ ksw[bi]) | ((2 * ks) & 8)) * 16);
+                ldmatrix_x4(kf, kb[bi] + (ks >> 2) * a.plane_bytes + (((2 * ks) & 7) ^ ksw[bi]) * 16);
                 mma16816<T>(s[bi][0], qf[ks], kf[0], kf[1]);
                 mma16816<T>(s[bi][1], qf[ks], kf[2], kf[3]);
             }
@@ -257,8 +295,10 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
         pa[bi][3] = pack2<T>(s[bi][1][2] * i1, s[bi][1][3] * i1);
     }
 
-    cp_async_wait<0>();
-    __syncthreads();                         // V has landed
+    if (!__syncthreads_and(mbar_wait0(mbV))) {        // V has landed
+        if (tid == 0) atomicAdd(&g_fwd128_wait_expired, 1u);
+        return;
+    }
 
     // ---------------------------------------------------------------- O = P V
     float o[D / 8][4];
@@ -268,12 +308,12 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
     for (int bi = 0; bi < NB; ++bi) {
         if (bi < nblk) {
             const int vrow = key_row(bi, (lane & 7) + 8 * ((lane >> 3) & 1));
-            const uint32_t vb = smem_u32(Vs + (size_t)vrow * PITCH);
+            const uint32_t vb = smem_u32(Vs + (size_t)vrow * 128);
             const int vsw = ((lane >> 4) ^ vrow) & 7;
 #pragma unroll
             for (int dp = 0; dp < D / 16; ++dp) {
                 uint32_t vf[4];
-                ldmatrix_x4_trans(vf, vb + ((((2 * dp) & 7) ^ vsw) | ((2 * dp) & 8)) * 16);
+                ldmatrix_x4_trans(vf, vb + (dp >> 2) * a.plane_bytes + (((2 * dp) & 7) ^ vsw) * 16);
                 mma16816<T>(o[2 * dp], pa[bi], vf[0], vf[1]);
                 mma16816<T>(o[2 * dp + 1], pa[bi], vf[2], vf[3]);
             }
@@ -303,6 +343,30 @@ span_fwd_tc128_kernel(SpanTc128Args a) {
 
 using namespace hsa;
 
+extern "C" int hsa_span_attn_fwd_wait_expired(unsigned int *count) {
+    if (count == nullptr) return fail(HSA_ERR_ARG, "hsa_span_attn_fwd_wait_expired: null pointer");
+    cudaError_t e = cudaMemcpyFromSymbol(count, g_fwd128_wait_expired, sizeof(unsigned int));
+    return e == cudaSuccess ? 0 : fail((int)e, "hsa_span_attn_fwd_wait_expired: %s", cudaGetErrorString(e));
+}
+
+// ---- tensor maps -------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against the driver library)
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
 // Shapes the 128-leaf-tile forward takes (a subset of what span_attn_fwd_tc.cu takes).
 bool hsa_span_attn_fwd_tc128_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, int B, int N, int H, int D,
                                        int radius, int causal, int dtype) {
@@ -317,18 +381,68 @@ bool hsa_span_attn_fwd_tc128_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_v
     if (B < 1 || H < 1) return false;
     if ((int64_t)(N / kT128) * H * B > 0x7fffffffLL) return false;
     if (!view_vec_ok(Q, 2) || !view_vec_ok(K, 2) || !view_vec_ok(V, 2) || !view_vec_ok(Out, 2)) return false;
+    // tensor maps: heads packed inside a row, strides within the descriptor's range, and a driver that has them
+    if (K.row_stride < (int64_t)H * D || V.row_stride < (int64_t)H * D) return false;
+    if (K.row_stride * 4 >= (1LL << 40) || V.row_stride * 4 >= (1LL << 40)) return false;
+    if (B > 1 && (K.batch_stride * 2 >= (1LL << 40) || V.batch_stride * 2 >= (1LL << 40))) return false;
+    if (B > 1 && (K.batch_stride < (int64_t)(2 * N - 1) * K.row_stride || V.batch_stride < (int64_t)(2 * N - 1) * V.row_stride))
+        return false;
+    return encode_tiled() != nullptr;
+}
+
+// A view [B, rows, H, D] of 2-byte elements, every `step`-th row, box = 64 elements x 1 head x box_rows rows.
+static bool make_map(CUtensorMap *m, const hsa_view &v, int B, int rows, int H, int D, int step, int box_rows) {
+    const cuuint64_t rows_eff = (cuuint64_t)(rows + step - 1) / step;
+    const cuuint64_t row_bytes = (cuuint64_t)v.row_stride * 2 * step;
+    cuuint64_t batch_bytes = (cuuint64_t)v.batch_stride * 2;
+    if (B == 1) batch_bytes = rows_eff * row_bytes;      // only batch 0 is addressed; any valid stride will do
+    const cuuint64_t gdim[4] = {(cuuint64_t)D, (cuuint64_t)H, rows_eff, (cuuint64_t)B};
+    const cuuint64_t gstride[3] = {(cuuint64_t)D * 2, row_bytes, batch_bytes};
+    const cuuint32_t box[4] = {64u, 1u, (cuuint32_t)box_rows, 1u};
+    const cuuint32_t estride[4] = {1u, 1u, 1u, 1u};
+    return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void *>(v.ptr), gdim, gstride, box, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The seven maps of one tensor; the last result is kept per calling thread (a training or benchmark loop calls
+// with the same buffers again and again).
+struct MapKey {
+    const void *ptr;
+    int64_t bs, rs;
+    int B, rows, H, D, band_rows;
+    bool operator==(const MapKey &o) const {
+        return ptr == o.ptr && bs == o.bs && rs == o.rs && B == o.B && rows == o.rows && H == o.H && D == o.D &&
+               band_rows == o.band_rows;
+    }
+};
+static bool tensor_maps(const hsa_view &v, int B, int N, int H, int D, int band_rows, int which, SpanTc128Maps *out) {
+    thread_local MapKey keys[2] = {};
+    thread_local SpanTc128Maps cached[2];
+    thread_local bool valid[2] = {false, false};
+    const MapKey key{v.ptr, v.batch_stride, v.row_stride, B, 2 * N - 1, H, D, band_rows};
+    if (!(valid[which] && keys[which] == key)) {
+        SpanTc128Maps m;
+        bool ok = make_map(&m.band, v, B, 2 * N - 1, H, D, 1, band_rows) && make_map(&m.one, v, B, 2 * N - 1, H, D, 1, 1);
+        for (int l = 1; l <= 5 && ok; ++l) ok = make_map(&m.even[l - 1], v, B, 2 * N - 1, H, D, 2, 64 >> l);
+        if (!ok) return false;
+        cached[which] = m;
+        keys[which] = key;
+        valid[which] = true;
+    }
+    *out = cached[which];
     return true;
 }
 
 template <typename T, int D>
-static int launch_tc128(const SpanTc128Args &a, int B, cudaStream_t st) {
-    const size_t smem = (size_t)2 * a.kv_rows * (D * 2);
+static int launch_tc128(const SpanTc128Args &a, const SpanTc128Maps &km, const SpanTc128Maps &vm, int B, cudaStream_t st) {
+    const size_t smem = (size_t)2 * (D / 64) * a.plane_bytes + 16 + 1024;     // planes, two mbarriers, alignment slack
     const int64_t total = (int64_t)B * (a.N / kT128) * a.H;
     const int nblk = (a.RB + 1) + ((a.L + 3 + 15) >> 4);
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_fwd(tc128): shared memory %zu: %s", smem, cudaGetErrorString(e));
-        kernel<<<(unsigned)total, 256, smem, st>>>(a);
+        kernel<<<(unsigned)total, 256, smem, st>>>(a, km, vm);
         return launch_status("hsa_span_attn_fwd(tc128)");
     };
     return nblk <= 3 ? go(span_fwd_tc128_kernel<T, D, 3>) : go(span_fwd_tc128_kernel<T, D, 4>);
@@ -346,7 +460,12 @@ int hsa_span_attn_fwd_tc128(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, fl
     a.RB = (radius + 15) / 16;
     a.band_rows = kT128 + 16 * a.RB;
     a.kv_rows = a.band_rows + kT128In + (a.L - kT128Log);
+    a.plane_bytes = (a.kv_rows + 7) / 8 * 8 * 128;
     a.scale_log2e = 1.4426950408889634f / sqrtf((float)D);
-    if (dtype == HSA_BF16) return D == 128 ? launch_tc128<__nv_bfloat16, 128>(a, B, st) : launch_tc128<__nv_bfloat16, 64>(a, B, st);
-    return D == 128 ? launch_tc128<__half, 128>(a, B, st) : launch_tc128<__half, 64>(a, B, st);
+    SpanTc128Maps km, vm;
+    if (!tensor_maps(K, B, N, H, D, a.band_rows, 0, &km) || !tensor_maps(V, B, N, H, D, a.band_rows, 1, &vm))
+        return fail(HSA_ERR_ARG, "hsa_span_attn_fwd(tc128): the driver refused a tensor map for these views");
+    if (dtype == HSA_BF16)
+        return D == 128 ? launch_tc128<__nv_bfloat16, 128>(a, km, vm, B, st) : launch_tc128<__nv_bfloat16, 64>(a, km, vm, B, st);
+    return D == 128 ? launch_tc128<__half, 128>(a, km, vm, B, st) : launch_tc128<__half, 64>(a, km, vm, B, st);
 }

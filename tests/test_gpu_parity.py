@@ -554,3 +554,16 @@ def test_layer_norm_vs_torch(hsa, shape, dtype):
     # widths the kernel does not take still work (library fallback)
     odd = LayerNorm(100).cuda()
     assert odd(torch.randn(3, 100, device="cuda")).shape == (3, 100)
+
+
+def test_forward_bulk_copy_waits_never_expire(hsa):
+    """The 128-leaf forward bounds its mbarrier waits; no CTA of any forward launched so far may have hit the bound."""
+    import ctypes
+    from sparseattention_b200 import _lib
+    from sparseattention_b200.ops import functional as F
+    q = torch.randn(2, 4096, 4, 128, device="cuda", dtype=torch.bfloat16)
+    kv = torch.randn(2, 8191, 4, 128, device="cuda", dtype=torch.bfloat16)
+    F.span_attention_forward(q, kv, kv, 16, True, algo=4)
+    count = ctypes.c_uint(123)
+    _lib.check(_lib.load().hsa_span_attn_fwd_wait_expired(ctypes.byref(count)), "hsa_span_attn_fwd_wait_expired")
+    assert count.value == 0
