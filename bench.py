@@ -45,7 +45,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel, measured with ncu on
 # `--workload layer_n4096_small` (profiles/), scaled by batch (traffic is proportional to batch).
-NCU_TRAFFIC_BYTES_PER_BATCH_ELEM = {"layer_n4096": 316.6e6 / 4, "layer_n4096_small": 316.6e6 / 4}
+NCU_TRAFFIC_BYTES_PER_BATCH_ELEM = {"layer_n4096": 317.2e6 / 4, "layer_n4096_small": 317.2e6 / 4}
 
 
 def measured_peaks():
