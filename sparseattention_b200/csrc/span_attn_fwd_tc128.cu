@@ -4,9 +4,7 @@
 // Same algorithm as span_attn_fwd_tc.cu, but a CTA covers 128 leaves with 8 warps and its K/V rows are
 // brought in by TMA (cp.async.bulk.tensor through tensor maps, completion on an mbarrier) instead of
 // per-thread cp.async: with no compute at all the per-thread copies top out at 5.4 TB/s on this access
-// pattern (the load/store pipe is the limiter), bulk copies reach 6.3 TB/s.  Q comes in the same way: its
-// 128 rows land where V will sit, every warp pulls its A fragments with ldmatrix, and only then are the V
-// boxes issued into those planes (V is not needed before the softmax is done).  A tile needs L boxes per
+// pattern (the load/store pipe is the limiter), bulk copies reach 6.3 TB/s.  A tile needs L boxes per
 // tensor and 128-byte half of the head dim: the leaf band, the left children of levels 1..5 (a second
 // tensor map over the even rows makes each level one box), the level-6 node and one node per upper level.
 // Rows land in [half][row][128 B] planes with the hardware's 128-byte swizzle, so ldmatrix is conflict
@@ -85,7 +83,7 @@ __device__ __forceinline__ int tree_slot128(int s, int w, int L, int &row, int &
 template <typename T, int D, int NB>      // NB: key blocks per warp the code is unrolled for (3 or 4)
 __global__ void __launch_bounds__(256, 2)
 span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Maps kmaps,
-                      const __grid_constant__ SpanTc128Maps vmaps, const __grid_constant__ CUtensorMap qmap) {
+                      const __grid_constant__ SpanTc128Maps vmaps) {
     constexpr int PITCH = D * 2;
     constexpr int CPR = D / 8;
     constexpr int KS = D / 16;
@@ -109,23 +107,26 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
     const int quad = lane & 3, qrow = lane >> 2;
     const int n0 = t0 + lw + qrow, n1 = n0 + 8;
 
-    // ---------------------------------------------------------------- stage Q (barrier 2), K (barrier 0), later V (barrier 1)
-    // Thread 0 announces the bytes of all boxes of a barrier; one thread per box issues it.  The 128 Q rows of
-    // the tile go where V will sit: once every warp has its Q fragments in registers the V boxes are issued
-    // into the same planes (V is not needed before the softmax is done).  Rows nobody may attend to are loaded
-    // all the same (upper levels on the causal side) or zero-filled by the copy engine (before the first leaf),
-    // so masked scores and 0 * V products stay finite.
-    const uint32_t mbK = smem_u32(&mbar[0]), mbV = smem_u32(&mbar[1]), mbQ = smem_u32(&mbar[2]);
+    // ---------------------------------------------------------------- stage K (barrier 0) and V (barrier 1)
+    // Thread 0 announces the bytes of all boxes; threads 0 .. 2*NH*L-1 issue one box each.  Rows nobody may
+    // attend to are loaded all the same (upper levels on the causal side) or zero-filled by the copy engine
+    // (before the first leaf), so masked scores and 0 * V products stay finite.
+    const uint32_t mbK = smem_u32(&mbar[0]), mbV = smem_u32(&mbar[1]);
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbK), "r"(1) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbV), "r"(1) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbQ), "r"(1) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
-    const uint32_t kv_bytes = (uint32_t)a.kv_rows * 128u * NH;
-    // box j of half hf of K or V (see the kernel's header comment for the list of boxes)
-    auto issue_kv_box = [&](const SpanTc128Maps &maps, unsigned char *S, uint32_t mb, int hf, int j) {
+    if (tid == 0) {
+        const uint32_t bytes = (uint32_t)a.kv_rows * 128u * NH;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbK), "r"(bytes) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV), "r"(bytes) : "memory");
+    }
+    if (tid < 2 * NH * L) {
+        const int isv = tid / (NH * L), rem = tid % (NH * L);       // K boxes first
+        const int hf = rem / L, j = rem % L;
+        const SpanTc128Maps &maps = isv ? vmaps : kmaps;
         const CUtensorMap *map;
         int row, dst_row;
         if (j == 0) {                                              // the leaf band
@@ -137,20 +138,24 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
         } else {                                                   // the sibling of the tile's ancestor at level j
             map = &maps.one; row = level_base(N, j) + ((t0 >> j) ^ 1); dst_row = a.band_rows + kT128In + (j - kT128Log);
         }
-        const uint32_t dst = smem_u32(S + (size_t)hf * a.plane_bytes + (size_t)dst_row * 128);
+        const uint32_t dst = smem_u32((isv ? Vs : Ks) + (size_t)hf * a.plane_bytes + (size_t)dst_row * 128);
         asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
-                     ::"r"(dst), "l"(map), "r"(64 * hf), "r"(h), "r"(row), "r"(b), "r"(mb) : "memory");
-    };
-    if (tid == 0) {
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbQ), "r"(kT128 * 128u * NH) : "memory");
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbK), "r"(kv_bytes) : "memory");
+                     ::"r"(dst), "l"(map), "r"(64 * hf), "r"(h), "r"(row), "r"(b), "r"(isv ? mbV : mbK) : "memory");
     }
-    if (tid < NH) {                                                // Q first: it is needed first
-        const uint32_t dst = smem_u32(Vs + (size_t)tid * a.plane_bytes);
-        asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
-                     ::"r"(dst), "l"(&qmap), "r"(64 * tid), "r"(h), "r"(t0), "r"(b), "r"(mbQ) : "memory");
-    } else if (tid >= 32 && tid < 32 + NH * L) {
-        issue_kv_box(kmaps, Ks, mbK, (tid - 32) / L, (tid - 32) % L);
+
+    // ---------------------------------------------------------------- Q: global -> A-operand registers
+    // (after the K/V copies have been handed to the copy engine)
+    uint32_t qf[KS][4];
+    {
+        const T *q0 = (const T *)a.q + b * a.q_bs + hoff + (int64_t)n0 * a.q_rs + 2 * quad;
+        const T *q1 = q0 + 8 * a.q_rs;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = ldg32(q0 + ks * 16);
+            qf[ks][1] = ldg32(q1 + ks * 16);
+            qf[ks][2] = ldg32(q0 + ks * 16 + 8);
+            qf[ks][3] = ldg32(q1 + ks * 16 + 8);
+        }
     }
 
     const int nbb = RB + 1;                 // band blocks: [the warp's own 16 leaves] (+ the 16 before them)
@@ -184,28 +189,6 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
         tree_slot128(16 * (o - nbb) + kk, warp, L, row, jj);
         return a.band_rows + row;
     };
-
-    // ---------------------------------------------------------------- Q: shared memory -> A-operand registers, then V
-    uint32_t qf[KS][4];
-    const bool q_ok = mbar_wait0(mbQ);
-    if (q_ok) {
-        const int qr = lw + (lane & 7) + 8 * ((lane >> 3) & 1);
-        const uint32_t qb = smem_u32(Vs + (size_t)qr * 128);
-        const int qsw = ((lane >> 4) ^ qr) & 7;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) ldmatrix_x4(qf[ks], qb + (ks >> 2) * a.plane_bytes + (((2 * ks) & 7) ^ qsw) * 16);
-    }
-    if (!__syncthreads_and(q_ok)) {                   // every warp holds its Q fragments: the planes are free for V
-        if (tid == 0) atomicAdd(&g_fwd128_wait_expired, 1u);
-        mbar_wait0(mbK);                              // a second bounded chance for this CTA's copies to finish
-        return;
-    }
-    if (tid == 0)
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV), "r"(kv_bytes) : "memory");
-    if (tid >= 64 && tid < 64 + NH * L) {
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // the reads of Q above come before these writes
-        issue_kv_box(vmaps, Vs, mbV, (tid - 64) / L, (tid - 64) % L);
-    }
 
     if (!__syncthreads_and(mbar_wait0(mbK))) {        // K has landed (the wait is not expected to give up)
         if (tid == 0) atomicAdd(&g_fwd128_wait_expired, 1u);
@@ -399,9 +382,7 @@ bool hsa_span_attn_fwd_tc128_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_v
     if ((int64_t)(N / kT128) * H * B > 0x7fffffffLL) return false;
     if (!view_vec_ok(Q, 2) || !view_vec_ok(K, 2) || !view_vec_ok(V, 2) || !view_vec_ok(Out, 2)) return false;
     // tensor maps: heads packed inside a row, strides within the descriptor's range, and a driver that has them
-    if (K.row_stride < (int64_t)H * D || V.row_stride < (int64_t)H * D || Q.row_stride < (int64_t)H * D) return false;
-    if (Q.row_stride * 2 >= (1LL << 40) || (B > 1 && (Q.batch_stride * 2 >= (1LL << 40) || Q.batch_stride < (int64_t)N * Q.row_stride)))
-        return false;
+    if (K.row_stride < (int64_t)H * D || V.row_stride < (int64_t)H * D) return false;
     if (K.row_stride * 4 >= (1LL << 40) || V.row_stride * 4 >= (1LL << 40)) return false;
     if (B > 1 && (K.batch_stride * 2 >= (1LL << 40) || V.batch_stride * 2 >= (1LL << 40))) return false;
     if (B > 1 && (K.batch_stride < (int64_t)(2 * N - 1) * K.row_stride || V.batch_stride < (int64_t)(2 * N - 1) * V.row_stride))
@@ -453,31 +434,15 @@ static bool tensor_maps(const hsa_view &v, int B, int N, int H, int D, int band_
     return true;
 }
 
-// Q [B, N, H, D]: one box = the 128 rows of a tile x 64 elements of one head
-static bool q_tensor_map(const hsa_view &v, int B, int N, int H, int D, CUtensorMap *out) {
-    thread_local MapKey key = {};
-    thread_local CUtensorMap cached;
-    thread_local bool valid = false;
-    const MapKey k{v.ptr, v.batch_stride, v.row_stride, B, N, H, D, kT128};
-    if (!(valid && key == k)) {
-        CUtensorMap m;
-        if (!make_map(&m, v, B, N, H, D, 1, kT128)) return false;
-        cached = m; key = k; valid = true;
-    }
-    *out = cached;
-    return true;
-}
-
 template <typename T, int D>
-static int launch_tc128(const SpanTc128Args &a, const SpanTc128Maps &km, const SpanTc128Maps &vm, const CUtensorMap &qm, int B,
-                        cudaStream_t st) {
-    const size_t smem = (size_t)2 * (D / 64) * a.plane_bytes + 32 + 1024;     // planes, three mbarriers, alignment slack
+static int launch_tc128(const SpanTc128Args &a, const SpanTc128Maps &km, const SpanTc128Maps &vm, int B, cudaStream_t st) {
+    const size_t smem = (size_t)2 * (D / 64) * a.plane_bytes + 16 + 1024;     // planes, two mbarriers, alignment slack
     const int64_t total = (int64_t)B * (a.N / kT128) * a.H;
     const int nblk = (a.RB + 1) + ((a.L + 3 + 15) >> 4);
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_fwd(tc128): shared memory %zu: %s", smem, cudaGetErrorString(e));
-        kernel<<<(unsigned)total, 256, smem, st>>>(a, km, vm, qm);
+        kernel<<<(unsigned)total, 256, smem, st>>>(a, km, vm);
         return launch_status("hsa_span_attn_fwd(tc128)");
     };
     return nblk <= 3 ? go(span_fwd_tc128_kernel<T, D, 3>) : go(span_fwd_tc128_kernel<T, D, 4>);
@@ -498,11 +463,9 @@ int hsa_span_attn_fwd_tc128(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, fl
     a.plane_bytes = (a.kv_rows + 7) / 8 * 8 * 128;
     a.scale_log2e = 1.4426950408889634f / sqrtf((float)D);
     SpanTc128Maps km, vm;
-    CUtensorMap qm;
-    if (!tensor_maps(K, B, N, H, D, a.band_rows, 0, &km) || !tensor_maps(V, B, N, H, D, a.band_rows, 1, &vm) ||
-        !q_tensor_map(Q, B, N, H, D, &qm))
+    if (!tensor_maps(K, B, N, H, D, a.band_rows, 0, &km) || !tensor_maps(V, B, N, H, D, a.band_rows, 1, &vm))
         return fail(HSA_ERR_ARG, "hsa_span_attn_fwd(tc128): the driver refused a tensor map for these views");
     if (dtype == HSA_BF16)
-        return D == 128 ? launch_tc128<__nv_bfloat16, 128>(a, km, vm, qm, B, st) : launch_tc128<__nv_bfloat16, 64>(a, km, vm, qm, B, st);
-    return D == 128 ? launch_tc128<__half, 128>(a, km, vm, qm, B, st) : launch_tc128<__half, 64>(a, km, vm, qm, B, st);
+        return D == 128 ? launch_tc128<__nv_bfloat16, 128>(a, km, vm, B, st) : launch_tc128<__nv_bfloat16, 64>(a, km, vm, B, st);
+    return D == 128 ? launch_tc128<__half, 128>(a, km, vm, B, st) : launch_tc128<__half, 64>(a, km, vm, B, st);
 }
