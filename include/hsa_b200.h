@@ -118,10 +118,10 @@ int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *L
                       int H, int D, int radius, int causal, int dtype, int algo, void *stream);
 
 /*
- * Diagnostic with no reference counterpart: the 128-leaf forward kernel waits for its bulk copies on an
- * mbarrier with a time limit (about a second); a CTA whose wait runs out counts itself here, skips its
- * tile and returns.  *count receives the number of such CTAs on the current device since the library was
- * loaded (0 in any healthy run).  Synchronises with the device (cudaMemcpyFromSymbol).
+ * Diagnostic with no reference counterpart: the TMA-staged kernels (128-leaf forward, 8-warp backward) wait
+ * for their bulk copies on mbarriers with a time limit (about a second); a CTA whose wait runs out counts
+ * itself, skips its tile and returns.  *count receives the number of such CTAs on the current device since
+ * the library was loaded (0 in any healthy run).  Synchronises with the device (cudaMemcpyFromSymbol).
  */
 int hsa_span_attn_fwd_wait_expired(unsigned int *count);
 

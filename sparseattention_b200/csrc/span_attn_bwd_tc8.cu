@@ -16,12 +16,22 @@
 //            block are stored, shared nodes go to fp32 partial rows that phase 5 combines in block order.
 //   phase 5  level-5 node, per-tile partial rows of the levels >= 6 (summed over tiles by a second kernel in
 //            tile order), zero rows for nodes nobody attends to.
-// Rows sit in shared memory at an unpadded pitch of 2*D bytes with XOR-swizzled 16-byte pieces.
+// Staged rows sit in [128-byte half][row][128 B] planes with the 128-byte XOR swizzle of the TMA unit: with 256-byte
+// rows (D = 128) one cp.async.bulk.tensor box per thread brings them in (bounded mbarrier waits), with 128-byte rows
+// per-thread cp.async does (the boxes would be too small to pay off).
 #include "tc_common.cuh"
+#include "tma_common.cuh"
 
 namespace hsa {
 
 constexpr int kBand8 = kTile + 16;      // staged rows per buffer: the tile and one 16-row block of halo
+
+// Tensor maps of the staged tensors, all over [B, rows, H, D] with a box of 64 elements of one head:
+// q, go: box of kBand8 rows; k/v band: every row, box of kBand8 rows; k/v e4, e2: every second row, boxes of 4 and 2
+// rows (the left children of levels 1 and 2 below a 16-leaf block); k/v one: every row, box of one row.
+struct SpanBwd8Maps {
+    CUtensorMap q, go, k_band, k_e4, k_e2, k_one, v_band, v_e4, v_e2, v_one;
+};
 
 struct SpanBwd8Args {
     const void *q, *k, *v, *out, *go;
@@ -32,14 +42,25 @@ struct SpanBwd8Args {
     int N, L, H, R;
     int ntb, tree_rows;
     int pf_dist;        // a CTA prefetches for CTA blockIdx.x + pf_dist
+    int mbar_off;
     // byte offsets into shared memory (the V band starts at 0)
     int kb_off, vt_off, kt_off, q_off, go_off, stat_off, tiles_off, ttiles_off, persist_off;
     float scale_log2e, scale;
 };
 
-// byte offset of 16-byte piece `piece_even` (+ the lane's piece parity, folded into x with row & 7) in a swizzled row
-__device__ __forceinline__ uint32_t piece_off(int piece_even, int x) {
-    return (uint32_t)((((piece_even & 7) ^ x) | (piece_even & 8)) * 16);
+// CTAs whose wait for their TMA copies ran out (never expected; added to what hsa_span_attn_fwd_wait_expired reports)
+__device__ unsigned int g_bwd8_wait_expired = 0;
+
+// Wait for phase 0 of an mbarrier, giving up after about a second.  Returns false when it gave up.
+__device__ __forceinline__ bool mbar8_wait0(uint32_t mb) {
+    uint32_t done = 0;
+    const long long start = clock64();
+    while (true) {
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done) : "r"(mb), "r"(0) : "memory");
+        if (done) return true;
+        if (clock64() - start > 2000000000LL) return false;
+    }
 }
 
 // Tree rows in shared memory: rows 8*qb .. 8*qb+7 hold what query block qb alone attends to (slots 0..7: four
@@ -65,8 +86,12 @@ __device__ __forceinline__ int tree_slot8(int s, int qb, int L, int &row, int &j
 
 template <typename T, int D>
 __global__ void __launch_bounds__(256, 2)
-span_bwd_tc8_kernel(SpanBwd8Args a) {
-    constexpr int PITCH = D * 2;
+span_bwd_tc8_kernel(const SpanBwd8Args a, const __grid_constant__ SpanBwd8Maps maps) {
+    constexpr int NH = D / 64;             // 128-byte halves of a row: buffers are [half][row][128 B] planes
+    // 256-byte rows come in by TMA; for 128-byte rows the boxes get so small (a 64-leaf tile needs 50 of them for half
+    // the bytes) that per-thread 16-byte copies are faster
+    constexpr bool TMA = D >= 128;
+    constexpr int BP = kBand8 * 128;       // bytes of one plane of a band buffer (Q, dOut, K band, V band)
     constexpr int CPR = D / 8;
     constexpr int RPI = 256 / CPR;
     constexpr int KS = D / 16;
@@ -74,7 +99,9 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
     constexpr int NTH = CW / 8;            // its 8-column n-tiles
     constexpr int FPS = 8;                 // first tree slot that is a partial sum (level 5)
     constexpr int PR = 2 * D + 8;          // floats per partial row (dK | dV), padded: 8 rows written at once spread over the banks
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the hardware swizzle of the TMA copies XORs address bits 4..6 with bits 7..9: keep the band planes on 1024 bytes
+    unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *Vb = smem;
     unsigned char *Kb = smem + a.kb_off;
     unsigned char *Vt = smem + a.vt_off;
@@ -88,6 +115,8 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
     unsigned char *tiles = smem + a.tiles_off;       // (kb, rel): P^T at ((kb*2+rel)*2), dS^T at +1; halo pair dS^T at 16
     unsigned char *ttiles = smem + a.ttiles_off;     // (qb, tb): P at ((qb*ntb+tb)*2), dS at +1   (inside the dead V band)
     float *persist = reinterpret_cast<float *>(smem + a.persist_off);   // [qb][1+nup] rows of PR floats, inside dead bands
+    unsigned long long *mbar = reinterpret_cast<unsigned long long *>(smem + a.mbar_off);
+    const int TP = a.tree_rows * 128;      // bytes of one plane of a tree buffer
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ntiles = a.N / kTile;
@@ -102,51 +131,117 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
     const int nup = L - kTileLog;
     const int nps = 1 + nup;
 
-    // ---------------------------------------------------------------- staging
+    // ---------------------------------------------------------------- staging: one TMA box per thread
+    // barrier 0: dOut; barrier 1: Q and the K/V bands; barrier 2: the tree rows.  Rows nobody may attend to are loaded
+    // all the same (level-4 siblings of even blocks, upper levels on the causal side) or zero-filled by the copy
+    // engine (past the last leaf, before the first), so masked scores and 0 * V products stay finite.
+    const uint32_t mbG = smem_u32(&mbar[0]), mbM = smem_u32(&mbar[1]), mbT = smem_u32(&mbar[2]);
+    // group 0: dOut, 1: Q and the bands, 2: the tree rows.  TMA: bounded mbarrier wait; per-thread copies: wait_group.
+    auto wait_group = [&](int g) -> bool {
+        if constexpr (TMA) {
+            return mbar8_wait0(g == 0 ? mbG : g == 1 ? mbM : mbT);
+        } else {
+            if (g == 0) cp_async_wait<2>(); else if (g == 1) cp_async_wait<1>(); else cp_async_wait<0>();
+            return true;
+        }
+    };
+    if (TMA && tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbG), "r"(1) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbM), "r"(1) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbT), "r"(1) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
     {
-        const int c = tid % CPR, rg = tid / CPR;               // RPI is a multiple of 8: (row & 7) == (rg & 7) on every pass
-        const int pc = ((c & ~7) | ((c ^ rg) & 7)) * 16;
-        auto stage_rows = [&](const void *base, int64_t bs, int64_t rs, unsigned char *S, int first) {
-            const T *gc = (const T *)base + b * bs + hoff + c * 8;
-            uint32_t dst = smem_u32(S) + rg * PITCH + pc;
-            int r = first + rg;
-            for (int i = rg; i < kBand8; i += RPI, r += RPI, dst += RPI * PITCH) {
-                const bool ok = (unsigned)r < (unsigned)N;
-                cp_async16(dst, gc + (int64_t)(ok ? r : 0) * rs, ok);
+        const int c = tid % CPR, rg = tid / CPR;
+        if constexpr (TMA) {
+            if (tid == 0) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbG), "r"((uint32_t)BP * NH) : "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbM), "r"(3u * BP * NH) : "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbT), "r"(2u * (uint32_t)TP * NH) : "memory");
             }
-        };
-        auto stage_tree = [&](const void *base, int64_t bs, int64_t rs, unsigned char *S) {
-            const T *gc = (const T *)base + b * bs + hoff + c * 8;
-            uint32_t dst = smem_u32(S) + rg * PITCH + pc;
-            for (int f = rg; f < a.tree_rows; f += RPI, dst += RPI * PITCH) {
-                int l, node;
-                bool ok = true;
-                if (f < 32) {
-                    const int qb = f >> 3, sl = f & 7;
-                    if (sl < 4) { l = 1; node = 8 * qb + 2 * sl; }
-                    else if (sl < 6) { l = 2; node = 4 * qb + 2 * (sl - 4); }
-                    else if (sl == 6) { l = 3; node = 2 * qb; }
-                    else { l = 4; node = qb ^ 1; ok = qb & 1; }          // the left sibling exists for odd blocks only
-                    node += t0 >> l;
-                } else if (f == 32) {
-                    l = 5; node = t0 >> 5;
+            // boxes per half: 0 dOut, 1 Q, 2 K band, 3 V band, then per tree tensor (K, V): 16 boxes of the four query
+            // blocks (level 1: 4 rows, level 2: 2 rows, level 3, level 4), the level-5 node, one node per upper level
+            const int per_tree = 17 + nup;
+            const int per_half = 4 + 2 * per_tree;
+            if (tid < NH * per_half) {
+                const int hf = tid / per_half, j = tid % per_half;
+                const CUtensorMap *map;
+                unsigned char *S;
+                int row, dst_row = 0;
+                uint32_t mb;
+                if (j < 4) {
+                    map = j == 0 ? &maps.go : j == 1 ? &maps.q : j == 2 ? &maps.k_band : &maps.v_band;
+                    S = (j == 0 ? Gs : j == 1 ? Qs : j == 2 ? Kb : Vb) + (size_t)hf * BP;
+                    row = j < 2 ? t0 : t0 - 16;
+                    mb = j == 0 ? mbG : mbM;
                 } else {
-                    l = kTileLog + (f - kTreeIn8);
-                    ok = (t0 >> l) & 1;
-                    node = (t0 >> l) ^ 1;
+                    const int isv = (j - 4) / per_tree, f = (j - 4) % per_tree;
+                    S = (isv ? Vt : Kt) + (size_t)hf * TP;
+                    mb = mbT;
+                    if (f < 16) {
+                        const int qb = f >> 2, kind = f & 3;
+                        if (kind == 0) { map = isv ? &maps.v_e4 : &maps.k_e4; row = (level_base(N, 1) + (t0 >> 1) + 8 * qb) >> 1; dst_row = 8 * qb; }
+                        else if (kind == 1) { map = isv ? &maps.v_e2 : &maps.k_e2; row = (level_base(N, 2) + (t0 >> 2) + 4 * qb) >> 1; dst_row = 8 * qb + 4; }
+                        else if (kind == 2) { map = isv ? &maps.v_one : &maps.k_one; row = level_base(N, 3) + (t0 >> 3) + 2 * qb; dst_row = 8 * qb + 6; }
+                        else { map = isv ? &maps.v_one : &maps.k_one; row = level_base(N, 4) + (t0 >> 4) + (qb ^ 1); dst_row = 8 * qb + 7; }
+                    } else if (f == 16) {
+                        map = isv ? &maps.v_one : &maps.k_one; row = level_base(N, 5) + (t0 >> 5); dst_row = 32;
+                    } else {
+                        const int l = kTileLog + (f - 17);
+                        map = isv ? &maps.v_one : &maps.k_one; row = level_base(N, l) + ((t0 >> l) ^ 1); dst_row = kTreeIn8 + (f - 17);
+                    }
                 }
-                cp_async16(dst, gc + (int64_t)(level_base(N, l) + node) * rs, ok);
+                const uint32_t dst = smem_u32(S + (size_t)dst_row * 128);
+                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+                             ::"r"(dst), "l"(map), "r"(64 * hf), "r"(h), "r"(row), "r"(b), "r"(mb) : "memory");
             }
-        };
-        stage_rows(a.go, a.go_bs, a.go_rs, Gs, t0);
-        cp_async_commit();
-        stage_rows(a.q, a.q_bs, a.q_rs, Qs, t0);
-        stage_rows(a.k, a.k_bs, a.k_rs, Kb, t0 - 16);
-        stage_rows(a.v, a.v_bs, a.v_rs, Vb, t0 - 16);
-        cp_async_commit();
-        stage_tree(a.k, a.k_bs, a.k_rs, Kt);                    // needed from the second phase on
-        stage_tree(a.v, a.v_bs, a.v_rs, Vt);
-        cp_async_commit();
+
+        } else {
+            // one 128-byte plane per buffer: per-thread 16-byte copies, pieces XORed with address bits 7..9 like the
+            // copy engine's swizzle.  Groups: dOut | Q and the bands | the tree rows.
+            auto put = [&](unsigned char *S, int row, const T *src, bool ok) {
+                const uint32_t ra = smem_u32(S + (size_t)row * 128);
+                cp_async16(ra + (((c ^ (ra >> 7)) & 7) << 4), src, ok);
+            };
+            auto stage_rows = [&](const void *base, int64_t bs, int64_t rs, unsigned char *S, int first) {
+                const T *gc = (const T *)base + b * bs + hoff + c * 8;
+                for (int i = rg; i < kBand8; i += RPI) {
+                    const int r = first + i;
+                    const bool ok = (unsigned)r < (unsigned)N;
+                    put(S, i, gc + (int64_t)(ok ? r : 0) * rs, ok);
+                }
+            };
+            auto stage_tree = [&](const void *base, int64_t bs, int64_t rs, unsigned char *S) {
+                const T *gc = (const T *)base + b * bs + hoff + c * 8;
+                for (int f = rg; f < a.tree_rows; f += RPI) {
+                    int l, node;
+                    if (f < 32) {
+                        const int qb = f >> 3, sl = f & 7;
+                        if (sl < 4) { l = 1; node = 8 * qb + 2 * sl; }
+                        else if (sl < 6) { l = 2; node = 4 * qb + 2 * (sl - 4); }
+                        else if (sl == 6) { l = 3; node = 2 * qb; }
+                        else { l = 4; node = qb ^ 1; }
+                        node += t0 >> l;
+                    } else if (f == 32) {
+                        l = 5; node = t0 >> 5;
+                    } else {
+                        l = kTileLog + (f - kTreeIn8);
+                        node = (t0 >> l) ^ 1;
+                    }
+                    put(S, f, gc + (int64_t)(level_base(N, l) + node) * rs, true);
+                }
+            };
+            stage_rows(a.go, a.go_bs, a.go_rs, Gs, t0);
+            cp_async_commit();
+            stage_rows(a.q, a.q_bs, a.q_rs, Qs, t0);
+            stage_rows(a.k, a.k_bs, a.k_rs, Kb, t0 - 16);
+            stage_rows(a.v, a.v_bs, a.v_rs, Vb, t0 - 16);
+            cp_async_commit();
+            stage_tree(a.k, a.k_bs, a.k_rs, Kt);
+            stage_tree(a.v, a.v_bs, a.v_rs, Vt);
+            cp_async_commit();
+        }
 
         // Pull the leaf rows of the tile that a later CTA will work on into L2, so that its staging pays L2 latency
         // instead of DRAM latency.  CTAs are handed out in blockIdx order and two are resident per SM: three
@@ -157,7 +252,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
                 const int h2 = (int)(nb % a.H);
                 const int tile2 = (int)((nb / a.H) % ntiles);
                 const int64_t b2 = nb / ((int64_t)a.H * ntiles);
-                constexpr int LPR = PITCH / 128;                       // 128-byte lines per row
+                constexpr int LPR = NH;                                // 128-byte lines per row
                 for (int i = tid; i < 5 * kTile * LPR; i += 256) {
                     const int which = i / (kTile * LPR), rem = i % (kTile * LPR);
                     const int64_t row = tile2 * kTile + rem / LPR;
@@ -196,14 +291,18 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
             ov[j] = ok ? __ldg(reinterpret_cast<const uint4 *>(og + (int64_t)n * a.o_rs + c * 8)) : make_uint4(0, 0, 0, 0);
             lv[j] = (ok && c == 0) ? __ldg(a.lse + ((int64_t)b * N + n) * a.H + h) * 1.4426950408889634f : INFINITY;
         }
-        cp_async_wait<2>();
-        __syncthreads();                                        // dOut rows are in shared memory
+        if (!__syncthreads_and(wait_group(0))) {              // dOut rows are in shared memory (the wait is not expected to give up)
+            if (tid == 0) atomicAdd(&g_bwd8_wait_expired, 1u);
+            wait_group(1);                                      // a second bounded chance for this CTA's copies to finish
+            wait_group(2);
+            return;
+        }
 #pragma unroll
         for (int j = 0; j < PF; ++j) {
             const int i = rg + j * RPI;
             float part = 0.f;
             if (i < kBand8) {
-                const uint4 gv = *reinterpret_cast<const uint4 *>(Gs + i * PITCH + pc);
+                const uint4 gv = *reinterpret_cast<const uint4 *>(Gs + (c >> 3) * BP + i * 128 + (((c ^ i) & 7) << 4));
                 const T *oe = reinterpret_cast<const T *>(&ov[j]);
                 const T *ge = reinterpret_cast<const T *>(&gv);
 #pragma unroll
@@ -216,46 +315,63 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
                 lse_s[i] = lv[j];
             }
         }
-        cp_async_wait<1>();
-        __syncthreads();
+        if (!__syncthreads_and(wait_group(1))) {              // Q and the bands have landed; the statistics are written
+            if (tid == 0) atomicAdd(&g_bwd8_wait_expired, 1u);
+            wait_group(2);
+            return;
+        }
     }
 
     const float c2 = a.scale_log2e, sc = a.scale;
+
+    // A row of a buffer for ldmatrix: per 128-byte half its shared address and the lane's piece parity folded into the
+    // row's swizzle (address bits 7..9).  X = plane 0 of the buffer, ps = bytes per plane.
+    struct RowRef { uint32_t addr[NH]; int x[NH]; };
+    auto row_ref = [&](const unsigned char *X, int ps, int row, int parity) {
+        RowRef r;
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) {
+            r.addr[hf] = smem_u32(X + (size_t)hf * ps + (size_t)row * 128);
+            r.x[hf] = (parity ^ (r.addr[hf] >> 7)) & 7;
+        }
+        return r;
+    };
+    // address of the 16-byte piece pe (even; the lane's parity is already in x) of the head dimension
+    auto piece_addr = [&](const RowRef &r, int pe) { return r.addr[pe >> 3] + (uint32_t)((((pe & 7) ^ r.x[pe >> 3])) << 4); };
 
     // Two 16x16 products over the whole head dimension that share their row patterns:
     //   r1 = A1[arow..] B1[brow..]^T,  r2 = A2[arow..] B2[brow..]^T.
     // arow / brow are this lane's ldmatrix rows (A: (lane&7)+8*((lane>>3)&1), pieces by lane>>4;
     // B: (lane&7)+8*(lane>>4), pieces by (lane>>3)&1).
     auto product2 = [&](const unsigned char *A1, const unsigned char *A2, int arow, const unsigned char *B1,
-                        const unsigned char *B2, int brow, float (&r1)[2][4], float (&r2)[2][4]) {
+                        const unsigned char *B2, int bps, int brow, float (&r1)[2][4], float (&r2)[2][4]) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) r1[0][e] = r1[1][e] = r2[0][e] = r2[1][e] = 0.f;
-        const uint32_t a1 = smem_u32(A1 + (size_t)arow * PITCH), a2 = smem_u32(A2 + (size_t)arow * PITCH);
-        const uint32_t b1 = smem_u32(B1 + (size_t)brow * PITCH), b2 = smem_u32(B2 + (size_t)brow * PITCH);
-        const int ax = ((lane >> 4) ^ arow) & 7, bx = (((lane >> 3) & 1) ^ brow) & 7;
+        const RowRef a1 = row_ref(A1, BP, arow, lane >> 4), a2 = row_ref(A2, BP, arow, lane >> 4);
+        const RowRef b1 = row_ref(B1, bps, brow, (lane >> 3) & 1), b2 = row_ref(B2, bps, brow, (lane >> 3) & 1);
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             uint32_t af[4], bf[4];
-            const uint32_t ao = piece_off(2 * ks, ax), bo = piece_off(2 * ks, bx);
-            ldmatrix_x4(af, a1 + ao);
-            ldmatrix_x4(bf, b1 + bo);
+            ldmatrix_x4(af, piece_addr(a1, 2 * ks));
+            ldmatrix_x4(bf, piece_addr(b1, 2 * ks));
             mma16816<T>(r1[0], af, bf[0], bf[1]);
             mma16816<T>(r1[1], af, bf[2], bf[3]);
-            ldmatrix_x4(af, a2 + ao);
-            ldmatrix_x4(bf, b2 + bo);
+            ldmatrix_x4(af, piece_addr(a2, 2 * ks));
+            ldmatrix_x4(bf, piece_addr(b2, 2 * ks));
             mma16816<T>(r2[0], af, bf[0], bf[1]);
             mma16816<T>(r2[1], af, bf[2], bf[3]);
         }
     };
     // acc[NTH][4] += A (16x16 register fragments) x rows (Bbuf, trow), columns [8*pb, 8*pb + CW).
     // trow is this lane's transposed-load row: (lane&7)+8*((lane>>3)&1), pieces by lane>>4.
-    auto accum_cols = [&](float (&acc)[NTH][4], const uint32_t (&af)[4], const unsigned char *Bbuf, int trow, int pb) {
-        const uint32_t tb = smem_u32(Bbuf + (size_t)trow * PITCH);
-        const int tx = ((lane >> 4) ^ trow) & 7;
+    auto accum_cols = [&](float (&acc)[NTH][4], const uint32_t (&af)[4], const unsigned char *Bbuf, int bps, int trow, int pb) {
+        // the CW columns of a task lie inside one 128-byte half
+        const uint32_t tb = smem_u32(Bbuf + (size_t)(pb >> 3) * bps + (size_t)trow * 128);
+        const int tx = ((lane >> 4) ^ (tb >> 7)) & 7;
 #pragma unroll
         for (int dp = 0; dp < CW / 16; ++dp) {
             uint32_t f[4];
-            ldmatrix_x4_trans(f, tb + piece_off(pb + 2 * dp, tx));
+            ldmatrix_x4_trans(f, tb + (uint32_t)(((((pb & 7) + 2 * dp)) ^ tx) << 4));
             mma16816<T>(acc[2 * dp], af, f[0], f[1]);
             mma16816<T>(acc[2 * dp + 1], af, f[2], f[3]);
         }
@@ -286,7 +402,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
     auto band_pair = [&](int kb, int rel, unsigned char *tile_p, unsigned char *tile_ds) {
         const int qr0 = 16 * (kb + rel);
         float st[2][4], dpt[2][4];
-        product2(Kb, Vb, 16 * (kb + 1) + (lane & 7) + 8 * ((lane >> 3) & 1), Qs, Gs, qr0 + (lane & 7) + 8 * (lane >> 4), st, dpt);
+        product2(Kb, Vb, 16 * (kb + 1) + (lane & 7) + 8 * ((lane >> 3) & 1), Qs, Gs, BP, qr0 + (lane & 7) + 8 * (lane >> 4), st, dpt);
         // element (nt, e): key row kr = qrow + 8*(e>>1), query column qc = nt*8 + 2*quad + (e&1)
         float p[2][4], ds[2][4];
 #pragma unroll
@@ -313,7 +429,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
         int rowA, jj;
         tree_slot8(16 * tb + (lane & 7) + 8 * (lane >> 4), qb, L, rowA, jj);
         float s[2][4], dp[2][4];
-        product2(Qs, Gs, 16 * qb + (lane & 7) + 8 * ((lane >> 3) & 1), Kt, Vt, rowA, s, dp);
+        product2(Qs, Gs, 16 * qb + (lane & 7) + 8 * ((lane >> 3) & 1), Kt, Vt, TP, rowA, s, dp);
         const float lse0 = lse_s[16 * qb + qrow], lse1 = lse_s[16 * qb + qrow + 8];
         const float dl0 = dl_s[16 * qb + qrow], dl1 = dl_s[16 * qb + qrow + 8];
         float p[2][4], ds[2][4];
@@ -350,7 +466,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
         for (int rel = 0; rel < 2; ++rel) {
             uint32_t af[4];
             tile_load(tiles + (size_t)((kb * 2 + rel) * 2 + (which ? 0 : 1)) * 512, af);
-            accum_cols(acc, af, which ? Gs : Qs, 16 * (kb + rel) + (lane & 7) + 8 * ((lane >> 3) & 1), ch * (CW / 8));
+            accum_cols(acc, af, which ? Gs : Qs, BP, 16 * (kb + rel) + (lane & 7) + 8 * ((lane >> 3) & 1), ch * (CW / 8));
         }
         T *g = which ? (T *)a.dv + b * a.dv_bs : (T *)a.dk + b * a.dk_bs;
         const int64_t rs = which ? a.dv_rs : a.dk_rs;
@@ -369,15 +485,15 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
         const int lrow = (lane & 7) + 8 * ((lane >> 3) & 1);
         if (qb > 0 || t0 > 0) {                                // keys of the block before the query block
             tile_load_t(qb == 0 ? tiles + 16 * 512 : tiles + (size_t)(((qb - 1) * 2 + 1) * 2 + 1) * 512, af);
-            accum_cols(acc, af, Kb, 16 * qb + lrow, pb);
+            accum_cols(acc, af, Kb, BP, 16 * qb + lrow, pb);
         }
         tile_load_t(tiles + (size_t)((qb * 2) * 2 + 1) * 512, af);     // keys of the query block itself
-        accum_cols(acc, af, Kb, 16 * (qb + 1) + lrow, pb);
+        accum_cols(acc, af, Kb, BP, 16 * (qb + 1) + lrow, pb);
         for (int tb = 0; tb < ntb; ++tb) {
             int rowB, jj;
             tree_slot8(16 * tb + lrow, qb, L, rowB, jj);
             tile_load(ttiles + (size_t)((qb * ntb + tb) * 2 + 1) * 512, af);
-            accum_cols(acc, af, Kt, rowB, pb);
+            accum_cols(acc, af, Kt, TP, rowB, pb);
         }
         T *g = (T *)a.dq + b * a.dq_bs + hoff + ch * CW;
         const int64_t r0 = t0 + 16 * qb + qrow;
@@ -392,7 +508,7 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
         for (int i = 0; i < NTH; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
         uint32_t af[4];
         tile_load_t(ttiles + (size_t)((qb * ntb + tb) * 2 + (which ? 0 : 1)) * 512, af);
-        accum_cols(acc, af, which ? Gs : Qs, 16 * qb + (lane & 7) + 8 * ((lane >> 3) & 1), ch * (CW / 8));
+        accum_cols(acc, af, which ? Gs : Qs, BP, 16 * qb + (lane & 7) + 8 * ((lane >> 3) & 1), ch * (CW / 8));
         // destinations of this thread's two slot rows (qrow and qrow + 8): nodes of levels 1..4 belong to this query
         // block alone; level 5 and above are partial sums
         T *fin[2] = {nullptr, nullptr};
@@ -429,8 +545,10 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
         unsigned char *tp = tiles + (size_t)((kb * 2 + rel) * 2) * 512;
         band_pair(kb, rel, tp, tp + 512);
     }
-    cp_async_wait<0>();     // the tree rows
-    __syncthreads();
+    if (!__syncthreads_and(wait_group(2))) {         // the tree rows
+        if (tid == 0) atomicAdd(&g_bwd8_wait_expired, 1u);
+        return;
+    }
     // ================================================================ phase 2
     if (warp < 4) {
         for (int tb = 0; tb < ntb; ++tb) tree_pair(warp, tb);
@@ -487,43 +605,89 @@ span_bwd_tc8_kernel(SpanBwd8Args a) {
 
 struct Bwd8Plan {
     int ntb, tree_rows, nup;
-    int kb_off, vt_off, kt_off, q_off, go_off, stat_off, tiles_off, ttiles_off, persist_off;
+    int kb_off, vt_off, kt_off, q_off, go_off, stat_off, tiles_off, ttiles_off, persist_off, mbar_off;
     size_t smem;
     bool fits;
 };
 
+// Shared-memory plan.  Every buffer is NH = D/64 planes of [rows][128 B]: V band, K band, V tree, K tree, then Q, dOut.
 static Bwd8Plan plan_bwd8(int N, int D) {
     Bwd8Plan p{};
-    const int PITCH = D * 2;
+    const int NH = D / 64;
+    const size_t BP = (size_t)kBand8 * 128;
     const int L = ilog2((unsigned)N);
     p.nup = L - kTileLog;
     p.ntb = (3 + L + 15) / 16;
     p.tree_rows = kTreeIn8 + p.nup;
+    const size_t TP = (size_t)p.tree_rows * 128;
     size_t off = 0;                                            // V band first: most of it is free after the first phase
-    off += (size_t)kBand8 * PITCH;
-    p.kb_off = (int)off; off += (size_t)kBand8 * PITCH;
-    p.vt_off = (int)off; off += (size_t)p.tree_rows * PITCH;
-    p.kt_off = (int)off; off += (size_t)p.tree_rows * PITCH;
-    off = (off + 127) / 128 * 128;
+    off += NH * BP;
+    p.kb_off = (int)off; off += NH * BP;
+    p.vt_off = (int)off; off += NH * TP;
+    p.kt_off = (int)off; off += NH * TP;
+    off = (off + 1023) / 1024 * 1024;
     const size_t alias_end = off;
-    p.q_off = (int)off; off += (size_t)kBand8 * PITCH;
-    p.go_off = (int)off; off += (size_t)kBand8 * PITCH;
+    p.q_off = (int)off; off += NH * BP;
+    p.go_off = (int)off; off += NH * BP;
     p.stat_off = (int)off; off += (size_t)2 * kBand8 * sizeof(float);
     off = (off + 15) / 16 * 16;
     p.tiles_off = (int)off; off += (size_t)17 * 512;
-    p.smem = off;
-    // tree tiles and the partial slots reuse the V band behind its first 16 rows (and what follows it)
-    p.ttiles_off = 16 * PITCH;
-    p.persist_off = p.ttiles_off + p.ntb * 8 * 512;
+    p.mbar_off = (int)off; off += 32;
+    p.smem = off + 1024;                                       // slack to put the first plane on a 1024-byte boundary
+    // tree tiles reuse rows 16.. of the first V-band plane (its first 16 rows, in every plane, are still read by the
+    // pair that reaches into the previous tile); the partial slots reuse what follows that plane
+    p.ttiles_off = 16 * 128;
+    p.persist_off = (int)BP;
     const size_t persist = (size_t)4 * (1 + p.nup) * (2 * D + 8) * sizeof(float);
-    p.fits = p.ntb <= 2 && (size_t)p.ttiles_off + (size_t)p.ntb * 8 * 512 <= (size_t)kBand8 * PITCH &&
-             (size_t)p.persist_off + persist <= alias_end;
+    p.fits = p.ntb <= 2 && (size_t)p.ttiles_off + (size_t)p.ntb * 8 * 512 <= BP && (size_t)p.persist_off + persist <= alias_end;
     return p;
+}
+
+// The ten tensor maps of a call; the last result is kept per calling thread (a training loop calls with the same
+// buffers again and again).
+struct Bwd8MapKey {
+    const void *ptr[4];
+    int64_t stride[8];
+    int B, N, H, D;
+    bool operator==(const Bwd8MapKey &o) const {
+        for (int i = 0; i < 4; ++i) if (ptr[i] != o.ptr[i]) return false;
+        for (int i = 0; i < 8; ++i) if (stride[i] != o.stride[i]) return false;
+        return B == o.B && N == o.N && H == o.H && D == o.D;
+    }
+};
+static bool bwd8_maps(const hsa_view &Q, const hsa_view &K, const hsa_view &V, const hsa_view &dOut, int B, int N, int H, int D,
+                      SpanBwd8Maps *out) {
+    thread_local Bwd8MapKey key = {};
+    thread_local SpanBwd8Maps cached;
+    thread_local bool valid = false;
+    const Bwd8MapKey k{{Q.ptr, K.ptr, V.ptr, dOut.ptr},
+                       {Q.batch_stride, Q.row_stride, K.batch_stride, K.row_stride, V.batch_stride, V.row_stride,
+                        dOut.batch_stride, dOut.row_stride},
+                       B, N, H, D};
+    if (!(valid && key == k)) {
+        SpanBwd8Maps m;
+        const int R2 = 2 * N - 1;
+        const bool ok = make_map(&m.q, Q, B, N, H, D, 1, kBand8) && make_map(&m.go, dOut, B, N, H, D, 1, kBand8) &&
+                        make_map(&m.k_band, K, B, R2, H, D, 1, kBand8) && make_map(&m.v_band, V, B, R2, H, D, 1, kBand8) &&
+                        make_map(&m.k_e4, K, B, R2, H, D, 2, 4) && make_map(&m.v_e4, V, B, R2, H, D, 2, 4) &&
+                        make_map(&m.k_e2, K, B, R2, H, D, 2, 2) && make_map(&m.v_e2, V, B, R2, H, D, 2, 2) &&
+                        make_map(&m.k_one, K, B, R2, H, D, 1, 1) && make_map(&m.v_one, V, B, R2, H, D, 1, 1);
+        if (!ok) return false;
+        cached = m; key = k; valid = true;
+    }
+    *out = cached;
+    return true;
 }
 
 }  // namespace hsa
 
 using namespace hsa;
+
+// CTAs of the 8-warp backward whose bounded wait for their TMA copies ran out (read by hsa_span_attn_fwd_wait_expired)
+int hsa_span_bwd8_wait_expired(unsigned int *count) {
+    cudaError_t e = cudaMemcpyFromSymbol(count, g_bwd8_wait_expired, sizeof(unsigned int));
+    return e == cudaSuccess ? 0 : fail((int)e, "hsa_span_attn_fwd_wait_expired: %s", cudaGetErrorString(e));
+}
 
 // Defined in span_attn_bwd_tc.cu: sums the tiles' partial rows of the nodes of level >= 6.
 int hsa_span_bwd_upper_reduce(float *partial, void *dk, void *dv, int64_t dk_bs, int64_t dk_rs, int64_t dv_bs, int64_t dv_rs,
@@ -539,18 +703,22 @@ bool hsa_span_attn_bwd_tc8_supported(const hsa_view *views, int nviews, int B, i
     if ((int64_t)(N / kTile) * H * B > 0x7fffffffLL) return false;
     for (int i = 0; i < nviews; ++i)
         if (!view_vec_ok(views[i], 2)) return false;
+    // views[]: Q, K, V, Out, dOut, dQ, dK, dV; the staged ones must be describable by tensor maps
+    if (D >= 128 && (nviews < 5 || !map_ok(views[0], B, N, H, D) || !map_ok(views[4], B, N, H, D) ||
+                     !map_ok(views[1], B, 2 * N - 1, H, D) || !map_ok(views[2], B, 2 * N - 1, H, D) || encode_tiled() == nullptr))
+        return false;
     const Bwd8Plan p = plan_bwd8(N, D);
     // worth it only while two CTAs fit on an SM (227 KB, 1 KB of it reserved per CTA)
     return p.fits && p.smem <= 115200;
 }
 
 template <typename T, int D>
-static int launch_bwd8(SpanBwd8Args &a, const Bwd8Plan &p, int B, cudaStream_t st) {
+static int launch_bwd8(SpanBwd8Args &a, const SpanBwd8Maps &maps, const Bwd8Plan &p, int B, cudaStream_t st) {
     const int64_t total = (int64_t)B * (a.N / kTile) * a.H;
     cudaError_t e = cudaFuncSetAttribute(span_bwd_tc8_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
     if (e != cudaSuccess)
         return fail((int)e, "hsa_span_attn_bwd(tc8): shared memory %zu: %s", p.smem, cudaGetErrorString(e));
-    span_bwd_tc8_kernel<T, D><<<(unsigned)total, 256, p.smem, st>>>(a);
+    span_bwd_tc8_kernel<T, D><<<(unsigned)total, 256, p.smem, st>>>(a, maps);
     return launch_status("hsa_span_attn_bwd(tc8)");
 }
 
@@ -578,13 +746,17 @@ int hsa_span_attn_bwd_tc8(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, cons
     }
     a.kb_off = p.kb_off; a.vt_off = p.vt_off; a.kt_off = p.kt_off; a.q_off = p.q_off; a.go_off = p.go_off;
     a.stat_off = p.stat_off; a.tiles_off = p.tiles_off; a.ttiles_off = p.ttiles_off; a.persist_off = p.persist_off;
+    a.mbar_off = p.mbar_off;
     a.scale = 1.0f / sqrtf((float)D);
     a.scale_log2e = 1.4426950408889634f * a.scale;
+    SpanBwd8Maps maps{};                                       // only the 256-byte-row kernel stages by TMA
+    if (D >= 128 && !bwd8_maps(Q, K, V, dOut, B, N, H, D, &maps))
+        return fail(HSA_ERR_ARG, "hsa_span_attn_bwd(tc8): the driver refused a tensor map for these views");
     int rc;
     if (dtype == HSA_BF16)
-        rc = D == 128 ? launch_bwd8<__nv_bfloat16, 128>(a, p, B, st) : launch_bwd8<__nv_bfloat16, 64>(a, p, B, st);
+        rc = D == 128 ? launch_bwd8<__nv_bfloat16, 128>(a, maps, p, B, st) : launch_bwd8<__nv_bfloat16, 64>(a, maps, p, B, st);
     else
-        rc = D == 128 ? launch_bwd8<__half, 128>(a, p, B, st) : launch_bwd8<__half, 64>(a, p, B, st);
+        rc = D == 128 ? launch_bwd8<__half, 128>(a, maps, p, B, st) : launch_bwd8<__half, 64>(a, maps, p, B, st);
     if (rc) return rc;
     return hsa_span_bwd_upper_reduce((float *)workspace, dK.ptr, dV.ptr, dK.batch_stride, dK.row_stride, dV.batch_stride,
                                      dV.row_stride, B, N, H, D, causal, dtype, st);

@@ -13,11 +13,8 @@
 // threads) the kernel scores all of a warp's key blocks first (at most two band blocks plus one tree block,
 // or two tree blocks once N > 8192), runs one softmax without rescaling, and normalises the probabilities
 // before P.V so the accumulators are final: the Q fragments are dead before the output accumulators live.
-#include <cuda.h>
-
-#include <mutex>
-
 #include "tc_common.cuh"
+#include "tma_common.cuh"
 
 namespace hsa {
 
@@ -343,28 +340,16 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
 
 using namespace hsa;
 
+int hsa_span_bwd8_wait_expired(unsigned int *count);        // span_attn_bwd_tc8.cu
+
 extern "C" int hsa_span_attn_fwd_wait_expired(unsigned int *count) {
     if (count == nullptr) return fail(HSA_ERR_ARG, "hsa_span_attn_fwd_wait_expired: null pointer");
-    cudaError_t e = cudaMemcpyFromSymbol(count, g_fwd128_wait_expired, sizeof(unsigned int));
-    return e == cudaSuccess ? 0 : fail((int)e, "hsa_span_attn_fwd_wait_expired: %s", cudaGetErrorString(e));
-}
-
-// ---- tensor maps -------------------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against the driver library)
-static EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
+    unsigned int fwd = 0, bwd = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&fwd, g_fwd128_wait_expired, sizeof(unsigned int));
+    if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_fwd_wait_expired: %s", cudaGetErrorString(e));
+    if (int rc = hsa_span_bwd8_wait_expired(&bwd)) return rc;
+    *count = fwd + bwd;
+    return 0;
 }
 
 // Shapes the 128-leaf-tile forward takes (a subset of what span_attn_fwd_tc.cu takes).
@@ -382,27 +367,8 @@ bool hsa_span_attn_fwd_tc128_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_v
     if ((int64_t)(N / kT128) * H * B > 0x7fffffffLL) return false;
     if (!view_vec_ok(Q, 2) || !view_vec_ok(K, 2) || !view_vec_ok(V, 2) || !view_vec_ok(Out, 2)) return false;
     // tensor maps: heads packed inside a row, strides within the descriptor's range, and a driver that has them
-    if (K.row_stride < (int64_t)H * D || V.row_stride < (int64_t)H * D) return false;
-    if (K.row_stride * 4 >= (1LL << 40) || V.row_stride * 4 >= (1LL << 40)) return false;
-    if (B > 1 && (K.batch_stride * 2 >= (1LL << 40) || V.batch_stride * 2 >= (1LL << 40))) return false;
-    if (B > 1 && (K.batch_stride < (int64_t)(2 * N - 1) * K.row_stride || V.batch_stride < (int64_t)(2 * N - 1) * V.row_stride))
-        return false;
+    if (!map_ok(K, B, 2 * N - 1, H, D) || !map_ok(V, B, 2 * N - 1, H, D)) return false;
     return encode_tiled() != nullptr;
-}
-
-// A view [B, rows, H, D] of 2-byte elements, every `step`-th row, box = 64 elements x 1 head x box_rows rows.
-static bool make_map(CUtensorMap *m, const hsa_view &v, int B, int rows, int H, int D, int step, int box_rows) {
-    const cuuint64_t rows_eff = (cuuint64_t)(rows + step - 1) / step;
-    const cuuint64_t row_bytes = (cuuint64_t)v.row_stride * 2 * step;
-    cuuint64_t batch_bytes = (cuuint64_t)v.batch_stride * 2;
-    if (B == 1) batch_bytes = rows_eff * row_bytes;      // only batch 0 is addressed; any valid stride will do
-    const cuuint64_t gdim[4] = {(cuuint64_t)D, (cuuint64_t)H, rows_eff, (cuuint64_t)B};
-    const cuuint64_t gstride[3] = {(cuuint64_t)D * 2, row_bytes, batch_bytes};
-    const cuuint32_t box[4] = {64u, 1u, (cuuint32_t)box_rows, 1u};
-    const cuuint32_t estride[4] = {1u, 1u, 1u, 1u};
-    return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void *>(v.ptr), gdim, gstride, box, estride,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // The seven maps of one tensor; the last result is kept per calling thread (a training or benchmark loop calls

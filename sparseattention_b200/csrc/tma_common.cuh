@@ -1,0 +1,53 @@
+// Tensor maps for the TMA-staged kernels: cuTensorMapEncodeTiled reached through the runtime's driver entry point
+// lookup (no link against the driver library), and the one map shape these kernels use.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "hsa_common.cuh"
+
+namespace hsa {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// A view [B, rows, H, D] of 2-byte elements, every `step`-th row; box = 64 elements x 1 head x box_rows rows,
+// 128-byte swizzle, rows outside the tensor read as zeros.
+inline bool make_map(CUtensorMap *m, const hsa_view &v, int B, int rows, int H, int D, int step, int box_rows) {
+    if (encode_tiled() == nullptr) return false;
+    const cuuint64_t rows_eff = (cuuint64_t)(rows + step - 1) / step;
+    const cuuint64_t row_bytes = (cuuint64_t)v.row_stride * 2 * step;
+    cuuint64_t batch_bytes = (cuuint64_t)v.batch_stride * 2;
+    if (B == 1) batch_bytes = rows_eff * row_bytes;      // only batch 0 is addressed; any valid stride will do
+    const cuuint64_t gdim[4] = {(cuuint64_t)D, (cuuint64_t)H, rows_eff, (cuuint64_t)B};
+    const cuuint64_t gstride[3] = {(cuuint64_t)D * 2, row_bytes, batch_bytes};
+    const cuuint32_t box[4] = {64u, 1u, (cuuint32_t)box_rows, 1u};
+    const cuuint32_t estride[4] = {1u, 1u, 1u, 1u};
+    return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void *>(v.ptr), gdim, gstride, box, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Whether a [B, rows, H, D] view can be described by such a map: heads packed inside a row, batches not overlapping,
+// strides inside the descriptor's 40-bit range.
+inline bool map_ok(const hsa_view &v, int B, int rows, int H, int D) {
+    if (v.row_stride < (int64_t)H * D || v.row_stride * 4 >= (1LL << 40)) return false;
+    if (B > 1 && (v.batch_stride * 2 >= (1LL << 40) || v.batch_stride < (int64_t)rows * v.row_stride)) return false;
+    return true;
+}
+
+}  // namespace hsa
