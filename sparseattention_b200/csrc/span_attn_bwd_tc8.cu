@@ -643,8 +643,8 @@ static Bwd8Plan plan_bwd8(int N, int D) {
     return p;
 }
 
-// The ten tensor maps of a call; the last result is kept per calling thread (a training loop calls with the same
-// buffers again and again).
+// The ten tensor maps of a call; the last sixteen results are kept per calling thread (a training loop calls with the
+// same buffers again and again).
 struct Bwd8MapKey {
     const void *ptr[4];
     int64_t stride[8];
@@ -657,25 +657,29 @@ struct Bwd8MapKey {
 };
 static bool bwd8_maps(const hsa_view &Q, const hsa_view &K, const hsa_view &V, const hsa_view &dOut, int B, int N, int H, int D,
                       SpanBwd8Maps *out) {
-    thread_local Bwd8MapKey key = {};
-    thread_local SpanBwd8Maps cached;
-    thread_local bool valid = false;
+    constexpr int kSlots = 16;                                 // a model's layers call with different buffers in turn
+    thread_local Bwd8MapKey keys[kSlots] = {};
+    thread_local SpanBwd8Maps cached[kSlots];
+    thread_local bool valid[kSlots] = {};
+    thread_local int next = 0;
     const Bwd8MapKey k{{Q.ptr, K.ptr, V.ptr, dOut.ptr},
                        {Q.batch_stride, Q.row_stride, K.batch_stride, K.row_stride, V.batch_stride, V.row_stride,
                         dOut.batch_stride, dOut.row_stride},
                        B, N, H, D};
-    if (!(valid && key == k)) {
-        SpanBwd8Maps m;
-        const int R2 = 2 * N - 1;
-        const bool ok = make_map(&m.q, Q, B, N, H, D, 1, kBand8) && make_map(&m.go, dOut, B, N, H, D, 1, kBand8) &&
-                        make_map(&m.k_band, K, B, R2, H, D, 1, kBand8) && make_map(&m.v_band, V, B, R2, H, D, 1, kBand8) &&
-                        make_map(&m.k_e4, K, B, R2, H, D, 2, 4) && make_map(&m.v_e4, V, B, R2, H, D, 2, 4) &&
-                        make_map(&m.k_e2, K, B, R2, H, D, 2, 2) && make_map(&m.v_e2, V, B, R2, H, D, 2, 2) &&
-                        make_map(&m.k_one, K, B, R2, H, D, 1, 1) && make_map(&m.v_one, V, B, R2, H, D, 1, 1);
-        if (!ok) return false;
-        cached = m; key = k; valid = true;
-    }
-    *out = cached;
+    for (int i = 0; i < kSlots; ++i)
+        if (valid[i] && keys[i] == k) { *out = cached[i]; return true; }
+    SpanBwd8Maps m;
+    const int R2 = 2 * N - 1;
+    const bool ok = make_map(&m.q, Q, B, N, H, D, 1, kBand8) && make_map(&m.go, dOut, B, N, H, D, 1, kBand8) &&
+                    make_map(&m.k_band, K, B, R2, H, D, 1, kBand8) && make_map(&m.v_band, V, B, R2, H, D, 1, kBand8) &&
+                    make_map(&m.k_e4, K, B, R2, H, D, 2, 4) && make_map(&m.v_e4, V, B, R2, H, D, 2, 4) &&
+                    make_map(&m.k_e2, K, B, R2, H, D, 2, 2) && make_map(&m.v_e2, V, B, R2, H, D, 2, 2) &&
+                    make_map(&m.k_one, K, B, R2, H, D, 1, 1) && make_map(&m.v_one, V, B, R2, H, D, 1, 1);
+    if (!ok) return false;
+    const int slot = next;
+    next = (next + 1) % kSlots;
+    cached[slot] = m; keys[slot] = k; valid[slot] = true;
+    *out = m;
     return true;
 }
 

@@ -371,7 +371,7 @@ bool hsa_span_attn_fwd_tc128_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_v
     return encode_tiled() != nullptr;
 }
 
-// The seven maps of one tensor; the last result is kept per calling thread (a training or benchmark loop calls
+// The seven maps of one tensor; the last results are kept per calling thread (a training or benchmark loop calls
 // with the same buffers again and again).
 struct MapKey {
     const void *ptr;
@@ -382,21 +382,23 @@ struct MapKey {
                band_rows == o.band_rows;
     }
 };
-static bool tensor_maps(const hsa_view &v, int B, int N, int H, int D, int band_rows, int which, SpanTc128Maps *out) {
-    thread_local MapKey keys[2] = {};
-    thread_local SpanTc128Maps cached[2];
-    thread_local bool valid[2] = {false, false};
+static bool tensor_maps(const hsa_view &v, int B, int N, int H, int D, int band_rows, SpanTc128Maps *out) {
+    constexpr int kSlots = 32;                                 // K and V of a model's layers, called in turn
+    thread_local MapKey keys[kSlots] = {};
+    thread_local SpanTc128Maps cached[kSlots];
+    thread_local bool valid[kSlots] = {};
+    thread_local int next = 0;
     const MapKey key{v.ptr, v.batch_stride, v.row_stride, B, 2 * N - 1, H, D, band_rows};
-    if (!(valid[which] && keys[which] == key)) {
-        SpanTc128Maps m;
-        bool ok = make_map(&m.band, v, B, 2 * N - 1, H, D, 1, band_rows) && make_map(&m.one, v, B, 2 * N - 1, H, D, 1, 1);
-        for (int l = 1; l <= 5 && ok; ++l) ok = make_map(&m.even[l - 1], v, B, 2 * N - 1, H, D, 2, 64 >> l);
-        if (!ok) return false;
-        cached[which] = m;
-        keys[which] = key;
-        valid[which] = true;
-    }
-    *out = cached[which];
+    for (int i = 0; i < kSlots; ++i)
+        if (valid[i] && keys[i] == key) { *out = cached[i]; return true; }
+    SpanTc128Maps m;
+    bool ok = make_map(&m.band, v, B, 2 * N - 1, H, D, 1, band_rows) && make_map(&m.one, v, B, 2 * N - 1, H, D, 1, 1);
+    for (int l = 1; l <= 5 && ok; ++l) ok = make_map(&m.even[l - 1], v, B, 2 * N - 1, H, D, 2, 64 >> l);
+    if (!ok) return false;
+    const int slot = next;
+    next = (next + 1) % kSlots;
+    cached[slot] = m; keys[slot] = key; valid[slot] = true;
+    *out = m;
     return true;
 }
 
@@ -429,7 +431,7 @@ int hsa_span_attn_fwd_tc128(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, fl
     a.plane_bytes = (a.kv_rows + 7) / 8 * 8 * 128;
     a.scale_log2e = 1.4426950408889634f / sqrtf((float)D);
     SpanTc128Maps km, vm;
-    if (!tensor_maps(K, B, N, H, D, a.band_rows, 0, &km) || !tensor_maps(V, B, N, H, D, a.band_rows, 1, &vm))
+    if (!tensor_maps(K, B, N, H, D, a.band_rows, &km) || !tensor_maps(V, B, N, H, D, a.band_rows, &vm))
         return fail(HSA_ERR_ARG, "hsa_span_attn_fwd(tc128): the driver refused a tensor map for these views");
     if (dtype == HSA_BF16)
         return D == 128 ? launch_tc128<__nv_bfloat16, 128>(a, km, vm, B, st) : launch_tc128<__nv_bfloat16, 64>(a, km, vm, B, st);
