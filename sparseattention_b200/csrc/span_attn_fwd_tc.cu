@@ -1,7 +1,9 @@
 // Span attention forward on tensor cores (bf16 / f16, head dim 64 or 128, N >= 64).
 //
 // One CTA = one (batch, head, aligned tile of 64 leaves), 4 warps of 16 leaves each.
-// The tile's whole key/value working set is staged in shared memory ONCE with 16-byte cp.async:
+// The tile's whole key/value working set is staged in shared memory ONCE, into [128-byte half][row][128 B]
+// planes with the 128-byte XOR swizzle of the TMA unit — by cp.async.bulk.tensor boxes (one per thread,
+// bounded mbarrier waits) when rows are 256 bytes, by per-thread 16-byte cp.async when they are 128 bytes:
 //   * the leaf band   [t0 - 16*RB, t0 + 64)            (RB = ceil(R/16); both sides when not causal)
 //   * the tree nodes inside the tile's subtree, levels 1..5 (only left children when causal:
 //     right children are never attended causally, so they are not even read from HBM)
@@ -14,6 +16,7 @@
 // inside the window; where both slots are valid its probability counts twice (reference semantics),
 // done by adding 1 to its base-2 logit.
 #include "tc_common.cuh"
+#include "tma_common.cuh"
 
 namespace hsa {
 
@@ -29,17 +32,43 @@ struct SpanTcArgs {
     float scale_log2e;
 };
 
+// Tensor maps of one tensor (K or V), all over [B, rows, H, D] with a box of 64 elements of one head:
+// band: every row, box of 16 rows; lv[l-1]: the box of the in-tile nodes of level l = 1..5 (causal: every second
+// row, 32 >> l rows; else every row, 64 >> l rows); one: every row, box of one row.
+struct SpanTcMaps {
+    CUtensorMap band, lv[5], one;
+};
+
+// CTAs whose wait for their TMA copies ran out (never expected; added to what hsa_span_attn_fwd_wait_expired reports)
+__device__ unsigned int g_fwd64_wait_expired = 0;
+
+__device__ __forceinline__ bool mbar64_wait0(uint32_t mb) {       // phase 0, giving up after about a second
+    uint32_t done = 0;
+    const long long start = clock64();
+    while (true) {
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done) : "r"(mb), "r"(0) : "memory");
+        if (done) return true;
+        if (clock64() - start > 2000000000LL) return false;
+    }
+}
+
 template <typename T, int D, bool CAUSAL>
 __global__ void __launch_bounds__(128, 3)
-span_fwd_tc_kernel(SpanTcArgs a) {
-    constexpr int PITCH = D * 2 + 16;          // bytes; the 16-byte skew keeps ldmatrix conflict-free
+span_fwd_tc_kernel(const SpanTcArgs a, const __grid_constant__ SpanTcMaps kmaps, const __grid_constant__ SpanTcMaps vmaps) {
+    constexpr int NH = D / 64;                 // 128-byte halves of a row
+    constexpr bool TMA = D >= 128;             // 128-byte rows: the boxes get too small to pay off
+    constexpr int OPITCH = D * 2 + 16;         // pitch of the output rows parked in shared memory (conflict-free skew)
     constexpr int CPR = D / 8;                 // 16-byte chunks per row
     constexpr int RPI = 128 / CPR;             // rows staged per pass of the CTA
     constexpr int KS = D / 16;                 // k-steps of the QK^T product
     constexpr int TIN = tree_in_rows<CAUSAL>();
-    extern __shared__ __align__(16) unsigned char smem[];
-    unsigned char *Ks = smem;
-    unsigned char *Vs = Ks + (size_t)a.kv_rows * PITCH;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    const int PS = a.kv_rows * 128;            // bytes of one plane
+    unsigned char *Ks = smem;                  // [NH][kv_rows][128 B]
+    unsigned char *Vs = Ks + (size_t)NH * PS;
+    unsigned long long *mbar = reinterpret_cast<unsigned long long *>(Vs + (size_t)NH * PS);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // work item id -> (batch, tile, head); heads vary fastest so that CTAs running together touch
@@ -75,21 +104,70 @@ span_fwd_tc_kernel(SpanTcArgs a) {
     }
 
     // ---------------------------------------------------------------- stage K (group 0) and V (group 1)
-    {
+    // Rows nobody may attend to are loaded all the same (upper levels on the causal side) or zero-filled (before the
+    // first leaf), so masked scores and 0 * V products stay finite.
+    const uint32_t mbK = smem_u32(&mbar[0]), mbV = smem_u32(&mbar[1]);
+    auto wait_group = [&](int g) -> bool {                       // 0: K, 1: V
+        if constexpr (TMA) {
+            return mbar64_wait0(g == 0 ? mbK : mbV);
+        } else {
+            if (g == 0) cp_async_wait<1>(); else cp_async_wait<0>();
+            return true;
+        }
+    };
+    if constexpr (TMA) {
+        if (tid == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbK), "r"(1) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbV), "r"(1) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        }
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t bytes = (uint32_t)PS * NH;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbK), "r"(bytes) : "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV), "r"(bytes) : "memory");
+        }
+        // boxes of one tensor and half: band_rows / 16 band boxes, one box per level 1..5, one node per upper level
+        const int nband = a.band_rows >> 4;
+        const int per = nband + 5 + (L - kTileLog);
+        for (int t = tid; t < 2 * NH * per; t += 128) {
+            const int isv = t / (NH * per), rem = t % (NH * per);     // K boxes first
+            const int hf = rem / per, j = rem % per;
+            const SpanTcMaps &maps = isv ? vmaps : kmaps;
+            const CUtensorMap *map;
+            int row, dst_row;
+            if (j < nband) {
+                map = &maps.band; row = band_lo + 16 * j; dst_row = 16 * j;
+            } else if (j < nband + 5) {
+                const int l = j - nband + 1;
+                map = &maps.lv[l - 1];
+                row = level_base(N, l) + (t0 >> l);
+                if (CAUSAL) row >>= 1;                                 // index among the even rows
+                dst_row = a.band_rows + tree_level_off<CAUSAL>(l);
+            } else {
+                const int l = kTileLog + (j - nband - 5);
+                map = &maps.one; row = level_base(N, l) + ((t0 >> l) ^ 1); dst_row = a.band_rows + TIN + (l - kTileLog);
+            }
+            const uint32_t dst = smem_u32((isv ? Vs : Ks) + (size_t)hf * PS + (size_t)dst_row * 128);
+            asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+                         ::"r"(dst), "l"(map), "r"(64 * hf), "r"(h), "r"(row), "r"(b), "r"(isv ? mbV : mbK) : "memory");
+        }
+    } else {
         const int c = tid % CPR, rg = tid / CPR;
         const int ntree = TIN + (L - kTileLog);
+        auto put = [&](unsigned char *S, int row, const T *src, bool ok) {
+            const uint32_t ra = smem_u32(S + (size_t)row * 128);
+            cp_async16(ra + (((c ^ (ra >> 7)) & 7) << 4), src, ok);
+        };
         auto stage_kv = [&](const T *g, int64_t rs, unsigned char *S) {
             const T *gc = g + c * 8;
-            uint32_t dst = smem_u32(S) + rg * PITCH + c * 16;
-            int r = band_lo + rg;
-            for (int i = rg; i < a.band_rows; i += RPI, r += RPI, dst += RPI * PITCH) {
+            for (int i = rg; i < a.band_rows; i += RPI) {
+                const int r = band_lo + i;
                 const bool ok = (unsigned)r < (unsigned)N;
-                cp_async16(dst, gc + (int64_t)(ok ? r : 0) * rs, ok);
+                put(S, i, gc + (int64_t)(ok ? r : 0) * rs, ok);
             }
-            dst = smem_u32(S) + (a.band_rows + rg) * PITCH + c * 16;
-            for (int f = rg; f < ntree; f += RPI, dst += RPI * PITCH) {
+            for (int f = rg; f < ntree; f += RPI) {
                 int rr;
-                bool ok = true;
                 if (f < TIN) {
                     const int rem = (CAUSAL ? 32 : 64) - f;
                     const int l = (CAUSAL ? 5 : 6) - (31 - __clz(rem - 1));
@@ -97,10 +175,9 @@ span_fwd_tc_kernel(SpanTcArgs a) {
                     rr = level_base(N, l) + (t0 >> l) + (CAUSAL ? 2 * i : i);
                 } else {
                     const int l = kTileLog + (f - TIN);
-                    ok = !CAUSAL || ((t0 >> l) & 1);
                     rr = level_base(N, l) + ((t0 >> l) ^ 1);
                 }
-                cp_async16(dst, gc + (int64_t)rr * rs, ok);
+                put(S, a.band_rows + f, gc + (int64_t)rr * rs, true);
             }
         };
         stage_kv(kg, a.k_rs, Ks);
@@ -150,8 +227,25 @@ span_fwd_tc_kernel(SpanTcArgs a) {
         return a.band_rows + row;
     };
 
-    cp_async_wait<1>();
-    __syncthreads();
+    if (!__syncthreads_and(wait_group(0))) {             // K has landed (the wait is not expected to give up)
+        if (tid == 0) atomicAdd(&g_fwd64_wait_expired, 1u);
+        wait_group(1);                                    // a second bounded chance for this CTA's copies to finish
+        return;
+    }
+
+    // A row of K or V for ldmatrix: per 128-byte half its shared address and the lane's piece parity folded into the
+    // row's swizzle (address bits 7..9)
+    struct RowRef { uint32_t addr[NH]; int x[NH]; };
+    auto row_ref = [&](const unsigned char *X, int row, int parity) {
+        RowRef r;
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) {
+            r.addr[hf] = smem_u32(X + (size_t)hf * PS + (size_t)row * 128);
+            r.x[hf] = (parity ^ (r.addr[hf] >> 7)) & 7;
+        }
+        return r;
+    };
+    auto piece_addr = [&](const RowRef &r, int pe) { return r.addr[pe >> 3] + (uint32_t)(((pe & 7) ^ r.x[pe >> 3]) << 4); };
 
     const float c2 = a.scale_log2e;
     for (int c0 = 0; c0 < nblk; c0 += kChunk) {
@@ -163,11 +257,11 @@ span_fwd_tc_kernel(SpanTcArgs a) {
             for (int e = 0; e < 4; ++e) s[bi][0][e] = s[bi][1][e] = 0.f;
             if (c0 + bi < nblk) {
                 const int krow = key_row(c0 + bi, (lane & 7) + 8 * (lane >> 4));
-                const uint32_t kb = smem_u32(Ks + (size_t)krow * PITCH + ((lane >> 3) & 1) * 16);
+                const RowRef kb = row_ref(Ks, krow, (lane >> 3) & 1);
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
                     uint32_t kf[4];
-                    ldmatrix_x4(kf, kb + ks * 32);
+                    ldmatrix_x4(kf, piece_addr(kb, 2 * ks));
                     mma16816<T>(s[bi][0], qf[ks], kf[0], kf[1]);
                     mma16816<T>(s[bi][1], qf[ks], kf[2], kf[3]);
                 }
@@ -224,7 +318,10 @@ span_fwd_tc_kernel(SpanTcArgs a) {
         }
         m0 = mn0;
         m1 = mn1;
-        if (c0 == 0) { cp_async_wait<0>(); __syncthreads(); }       // V has landed
+        if (c0 == 0 && !__syncthreads_and(wait_group(1))) {        // V has landed
+            if (tid == 0) atomicAdd(&g_fwd64_wait_expired, 1u);
+            return;
+        }
         // ---- probabilities and P.V
 #pragma unroll
         for (int bi = 0; bi < kChunk; ++bi) {
@@ -245,11 +342,11 @@ span_fwd_tc_kernel(SpanTcArgs a) {
                 pa[2] = pack2<T>(p[1][0], p[1][1]);
                 pa[3] = pack2<T>(p[1][2], p[1][3]);
                 const int vrow = key_row(c0 + bi, (lane & 7) + 8 * ((lane >> 3) & 1));
-                const uint32_t vb = smem_u32(Vs + (size_t)vrow * PITCH + (lane >> 4) * 16);
+                const RowRef vb = row_ref(Vs, vrow, lane >> 4);
 #pragma unroll
                 for (int dp = 0; dp < D / 16; ++dp) {
                     uint32_t vf[4];
-                    ldmatrix_x4_trans(vf, vb + dp * 32);
+                    ldmatrix_x4_trans(vf, piece_addr(vb, 2 * dp));
                     mma16816<T>(o[2 * dp], pa, vf[0], vf[1]);
                     mma16816<T>(o[2 * dp + 1], pa, vf[2], vf[3]);
                 }
@@ -271,12 +368,12 @@ span_fwd_tc_kernel(SpanTcArgs a) {
     // When every warp is done with K, each warp parks its 16 output rows in K's first rows and then
     // stores them 16 bytes per lane (full 32-byte sectors, whole rows per request).
     __syncthreads();
-    unsigned char *Os = Ks + lw * PITCH;
+    unsigned char *Os = Ks + lw * OPITCH;
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
         const int col = nt * 8 + 2 * quad;
-        *reinterpret_cast<uint32_t *>(Os + qrow * PITCH + col * 2) = pack2<T>(o[nt][0] * i0, o[nt][1] * i0);
-        *reinterpret_cast<uint32_t *>(Os + (qrow + 8) * PITCH + col * 2) = pack2<T>(o[nt][2] * i1, o[nt][3] * i1);
+        *reinterpret_cast<uint32_t *>(Os + qrow * OPITCH + col * 2) = pack2<T>(o[nt][0] * i0, o[nt][1] * i0);
+        *reinterpret_cast<uint32_t *>(Os + (qrow + 8) * OPITCH + col * 2) = pack2<T>(o[nt][2] * i1, o[nt][3] * i1);
     }
     __syncwarp();
     T *og = (T *)a.out + b * a.o_bs + hoff;
@@ -284,20 +381,53 @@ span_fwd_tc_kernel(SpanTcArgs a) {
     for (int it = 0; it < (16 * CPR) / 32; ++it) {
         const int idx = it * 32 + lane;
         const int r = idx / CPR, c = idx % CPR;
-        const uint4 val = *reinterpret_cast<const uint4 *>(Os + r * PITCH + c * 16);
+        const uint4 val = *reinterpret_cast<const uint4 *>(Os + r * OPITCH + c * 16);
         *reinterpret_cast<uint4 *>(og + (int64_t)(t0 + lw + r) * a.o_rs + c * 8) = val;
     }
 }
 
+static size_t smem_bytes_tc(int D, int kv_rows) {            // planes of K and V, two mbarriers, alignment slack
+    return (size_t)2 * (D / 64) * kv_rows * 128 + 16 + 128;
+}
+
+// The seven maps of one tensor; the last results are kept per calling thread.
+struct TcMapKey {
+    const void *ptr;
+    int64_t bs, rs;
+    int B, rows, H, D, causal;
+    bool operator==(const TcMapKey &o) const {
+        return ptr == o.ptr && bs == o.bs && rs == o.rs && B == o.B && rows == o.rows && H == o.H && D == o.D && causal == o.causal;
+    }
+};
+static bool tc_tensor_maps(const hsa_view &v, int B, int N, int H, int D, bool causal, SpanTcMaps *out) {
+    constexpr int kSlots = 32;
+    thread_local TcMapKey keys[kSlots] = {};
+    thread_local SpanTcMaps cached[kSlots];
+    thread_local bool valid[kSlots] = {};
+    thread_local int next = 0;
+    const TcMapKey key{v.ptr, v.batch_stride, v.row_stride, B, 2 * N - 1, H, D, causal ? 1 : 0};
+    for (int i = 0; i < kSlots; ++i)
+        if (valid[i] && keys[i] == key) { *out = cached[i]; return true; }
+    SpanTcMaps m;
+    bool ok = make_map(&m.band, v, B, 2 * N - 1, H, D, 1, 16) && make_map(&m.one, v, B, 2 * N - 1, H, D, 1, 1);
+    for (int l = 1; l <= 5 && ok; ++l)
+        ok = causal ? make_map(&m.lv[l - 1], v, B, 2 * N - 1, H, D, 2, 32 >> l) : make_map(&m.lv[l - 1], v, B, 2 * N - 1, H, D, 1, 64 >> l);
+    if (!ok) return false;
+    const int slot = next;
+    next = (next + 1) % kSlots;
+    cached[slot] = m; keys[slot] = key; valid[slot] = true;
+    *out = m;
+    return true;
+}
+
 template <typename T, int D>
-static int launch_tc(const SpanTcArgs &a, int B, bool causal, cudaStream_t st) {
-    constexpr int PITCH = D * 2 + 16;
-    const size_t smem = (size_t)(2 * a.kv_rows) * PITCH;
+static int launch_tc(const SpanTcArgs &a, const SpanTcMaps &km, const SpanTcMaps &vm, int B, bool causal, cudaStream_t st) {
+    const size_t smem = smem_bytes_tc(D, a.kv_rows);
     const int64_t total = (int64_t)B * (a.N / kTile) * a.H;
     auto go = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_fwd(tc): shared memory %zu: %s", smem, cudaGetErrorString(e));
-        kernel<<<(unsigned)total, 128, smem, st>>>(a);
+        kernel<<<(unsigned)total, 128, smem, st>>>(a, km, vm);
         return launch_status("hsa_span_attn_fwd(tc)");
     };
     return causal ? go(span_fwd_tc_kernel<T, D, true>) : go(span_fwd_tc_kernel<T, D, false>);
@@ -321,8 +451,14 @@ bool hsa_span_attn_fwd_tc_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_view
     const int L = ilog2((unsigned)N);
     const int band = kTile + 16 * RB * (causal ? 1 : 2);
     const int kv = band + (causal ? 31 : 62) + (L - kTileLog);
-    const size_t smem = (size_t)(2 * kv) * (D * 2 + 16);
-    return smem <= 200 * 1024;
+    if (D >= 128 && (!map_ok(K, B, 2 * N - 1, H, D) || !map_ok(V, B, 2 * N - 1, H, D) || encode_tiled() == nullptr)) return false;
+    return smem_bytes_tc(D, kv) <= 200 * 1024;
+}
+
+// CTAs of this kernel whose bounded wait for their TMA copies ran out (read by hsa_span_attn_fwd_wait_expired)
+int hsa_span_fwd64_wait_expired(unsigned int *count) {
+    cudaError_t e = cudaMemcpyFromSymbol(count, g_fwd64_wait_expired, sizeof(unsigned int));
+    return e == cudaSuccess ? 0 : fail((int)e, "hsa_span_attn_fwd_wait_expired: %s", cudaGetErrorString(e));
 }
 
 int hsa_span_attn_fwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H, int D,
@@ -340,7 +476,10 @@ int hsa_span_attn_fwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float
     a.band_rows = kTile + 16 * a.RB * (causal ? 1 : 2);
     a.kv_rows = a.band_rows + (causal ? 31 : 62) + (a.L - kTileLog);
     a.scale_log2e = 1.4426950408889634f / sqrtf((float)D);
+    SpanTcMaps km{}, vm{};                                     // only the 256-byte-row kernel stages by TMA
+    if (D >= 128 && (!tc_tensor_maps(K, B, N, H, D, causal != 0, &km) || !tc_tensor_maps(V, B, N, H, D, causal != 0, &vm)))
+        return fail(HSA_ERR_ARG, "hsa_span_attn_fwd(tc): the driver refused a tensor map for these views");
     if (dtype == HSA_BF16)
-        return D == 128 ? launch_tc<__nv_bfloat16, 128>(a, B, causal != 0, st) : launch_tc<__nv_bfloat16, 64>(a, B, causal != 0, st);
-    return D == 128 ? launch_tc<__half, 128>(a, B, causal != 0, st) : launch_tc<__half, 64>(a, B, causal != 0, st);
+        return D == 128 ? launch_tc<__nv_bfloat16, 128>(a, km, vm, B, causal != 0, st) : launch_tc<__nv_bfloat16, 64>(a, km, vm, B, causal != 0, st);
+    return D == 128 ? launch_tc<__half, 128>(a, km, vm, B, causal != 0, st) : launch_tc<__half, 64>(a, km, vm, B, causal != 0, st);
 }

@@ -341,14 +341,16 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
 using namespace hsa;
 
 int hsa_span_bwd8_wait_expired(unsigned int *count);        // span_attn_bwd_tc8.cu
+int hsa_span_fwd64_wait_expired(unsigned int *count);       // span_attn_fwd_tc.cu
 
 extern "C" int hsa_span_attn_fwd_wait_expired(unsigned int *count) {
     if (count == nullptr) return fail(HSA_ERR_ARG, "hsa_span_attn_fwd_wait_expired: null pointer");
-    unsigned int fwd = 0, bwd = 0;
+    unsigned int fwd = 0, bwd = 0, fwd64 = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&fwd, g_fwd128_wait_expired, sizeof(unsigned int));
     if (e != cudaSuccess) return fail((int)e, "hsa_span_attn_fwd_wait_expired: %s", cudaGetErrorString(e));
     if (int rc = hsa_span_bwd8_wait_expired(&bwd)) return rc;
-    *count = fwd + bwd;
+    if (int rc = hsa_span_fwd64_wait_expired(&fwd64)) return rc;
+    *count = fwd + bwd + fwd64;
     return 0;
 }
 
