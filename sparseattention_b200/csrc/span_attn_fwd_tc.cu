@@ -29,11 +29,12 @@ struct SpanTcArgs {
     int RB;          // ceil(R / 16)
     int band_rows;   // leaf rows staged per tile
     int kv_rows;     // all rows staged per tile
+    int band_box;    // rows per TMA box of the leaf band (the whole band when it fits one box)
     float scale_log2e;
 };
 
 // Tensor maps of one tensor (K or V), all over [B, rows, H, D] with a box of 64 elements of one head:
-// band: every row, box of 16 rows; lv[l-1]: the box of the in-tile nodes of level l = 1..5 (causal: every second
+// band: every row, box of band_box rows; lv[l-1]: the box of the in-tile nodes of level l = 1..5 (causal: every second
 // row, 32 >> l rows; else every row, 64 >> l rows); one: every row, box of one row.
 struct SpanTcMaps {
     CUtensorMap band, lv[5], one;
@@ -128,7 +129,7 @@ span_fwd_tc_kernel(const SpanTcArgs a, const __grid_constant__ SpanTcMaps kmaps,
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV), "r"(bytes) : "memory");
         }
         // boxes of one tensor and half: band_rows / 16 band boxes, one box per level 1..5, one node per upper level
-        const int nband = a.band_rows >> 4;
+        const int nband = a.band_rows / a.band_box;
         const int per = nband + 5 + (L - kTileLog);
         for (int t = tid; t < 2 * NH * per; t += 128) {
             const int isv = t / (NH * per), rem = t % (NH * per);     // K boxes first
@@ -137,7 +138,7 @@ span_fwd_tc_kernel(const SpanTcArgs a, const __grid_constant__ SpanTcMaps kmaps,
             const CUtensorMap *map;
             int row, dst_row;
             if (j < nband) {
-                map = &maps.band; row = band_lo + 16 * j; dst_row = 16 * j;
+                map = &maps.band; row = band_lo + a.band_box * j; dst_row = a.band_box * j;
             } else if (j < nband + 5) {
                 const int l = j - nband + 1;
                 map = &maps.lv[l - 1];
@@ -394,22 +395,23 @@ static size_t smem_bytes_tc(int D, int kv_rows) {            // planes of K and 
 struct TcMapKey {
     const void *ptr;
     int64_t bs, rs;
-    int B, rows, H, D, causal;
+    int B, rows, H, D, causal, band_box;
     bool operator==(const TcMapKey &o) const {
-        return ptr == o.ptr && bs == o.bs && rs == o.rs && B == o.B && rows == o.rows && H == o.H && D == o.D && causal == o.causal;
+        return ptr == o.ptr && bs == o.bs && rs == o.rs && B == o.B && rows == o.rows && H == o.H && D == o.D && causal == o.causal &&
+               band_box == o.band_box;
     }
 };
-static bool tc_tensor_maps(const hsa_view &v, int B, int N, int H, int D, bool causal, SpanTcMaps *out) {
+static bool tc_tensor_maps(const hsa_view &v, int B, int N, int H, int D, bool causal, int band_box, SpanTcMaps *out) {
     constexpr int kSlots = 32;
     thread_local TcMapKey keys[kSlots] = {};
     thread_local SpanTcMaps cached[kSlots];
     thread_local bool valid[kSlots] = {};
     thread_local int next = 0;
-    const TcMapKey key{v.ptr, v.batch_stride, v.row_stride, B, 2 * N - 1, H, D, causal ? 1 : 0};
+    const TcMapKey key{v.ptr, v.batch_stride, v.row_stride, B, 2 * N - 1, H, D, causal ? 1 : 0, band_box};
     for (int i = 0; i < kSlots; ++i)
         if (valid[i] && keys[i] == key) { *out = cached[i]; return true; }
     SpanTcMaps m;
-    bool ok = make_map(&m.band, v, B, 2 * N - 1, H, D, 1, 16) && make_map(&m.one, v, B, 2 * N - 1, H, D, 1, 1);
+    bool ok = make_map(&m.band, v, B, 2 * N - 1, H, D, 1, band_box) && make_map(&m.one, v, B, 2 * N - 1, H, D, 1, 1);
     for (int l = 1; l <= 5 && ok; ++l)
         ok = causal ? make_map(&m.lv[l - 1], v, B, 2 * N - 1, H, D, 2, 32 >> l) : make_map(&m.lv[l - 1], v, B, 2 * N - 1, H, D, 1, 64 >> l);
     if (!ok) return false;
@@ -475,9 +477,10 @@ int hsa_span_attn_fwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float
     a.RB = (a.R + 15) / 16;
     a.band_rows = kTile + 16 * a.RB * (causal ? 1 : 2);
     a.kv_rows = a.band_rows + (causal ? 31 : 62) + (a.L - kTileLog);
+    a.band_box = a.band_rows <= 256 ? a.band_rows : 16;
     a.scale_log2e = 1.4426950408889634f / sqrtf((float)D);
     SpanTcMaps km{}, vm{};                                     // only the 256-byte-row kernel stages by TMA
-    if (D >= 128 && (!tc_tensor_maps(K, B, N, H, D, causal != 0, &km) || !tc_tensor_maps(V, B, N, H, D, causal != 0, &vm)))
+    if (D >= 128 && (!tc_tensor_maps(K, B, N, H, D, causal != 0, a.band_box, &km) || !tc_tensor_maps(V, B, N, H, D, causal != 0, a.band_box, &vm)))
         return fail(HSA_ERR_ARG, "hsa_span_attn_fwd(tc): the driver refused a tensor map for these views");
     if (dtype == HSA_BF16)
         return D == 128 ? launch_tc<__nv_bfloat16, 128>(a, km, vm, B, causal != 0, st) : launch_tc<__nv_bfloat16, 64>(a, km, vm, B, causal != 0, st);
