@@ -41,7 +41,6 @@ struct SpanBwd8Args {
     int64_t q_bs, q_rs, k_bs, k_rs, v_bs, v_rs, o_bs, o_rs, go_bs, go_rs, dq_bs, dq_rs, dk_bs, dk_rs, dv_bs, dv_rs;
     int N, L, H, R;
     int ntb, tree_rows;
-    int pf_dist;        // a CTA prefetches for CTA blockIdx.x + pf_dist
     int mbar_off;
     // byte offsets into shared memory (the V band starts at 0)
     int kb_off, vt_off, kt_off, q_off, go_off, stat_off, tiles_off, ttiles_off, persist_off;
@@ -241,41 +240,6 @@ span_bwd_tc8_kernel(const SpanBwd8Args a, const __grid_constant__ SpanBwd8Maps m
             stage_tree(a.k, a.k_bs, a.k_rs, Kt);
             stage_tree(a.v, a.v_bs, a.v_rs, Vt);
             cp_async_commit();
-        }
-
-        // Pull the leaf rows of the tile that a later CTA will work on into L2, so that its staging pays L2 latency
-        // instead of DRAM latency.  CTAs are handed out in blockIdx order and two are resident per SM: three
-        // quarters of the SM count ahead measured best (further ahead, lines are evicted again before their use).
-        {
-            const int64_t nb = (int64_t)blockIdx.x + a.pf_dist;
-            if (nb < (int64_t)gridDim.x) {
-                const int h2 = (int)(nb % a.H);
-                const int tile2 = (int)((nb / a.H) % ntiles);
-                const int64_t b2 = nb / ((int64_t)a.H * ntiles);
-                constexpr int LPR = NH;                                // 128-byte lines per row
-                for (int i = tid; i < 5 * kTile * LPR; i += 256) {
-                    const int which = i / (kTile * LPR), rem = i % (kTile * LPR);
-                    const int64_t row = tile2 * kTile + rem / LPR;
-                    const T *src;
-                    switch (which) {
-                        case 0: src = (const T *)a.go + b2 * a.go_bs + row * a.go_rs; break;
-                        case 1: src = (const T *)a.q + b2 * a.q_bs + row * a.q_rs; break;
-                        case 2: src = (const T *)a.k + b2 * a.k_bs + row * a.k_rs; break;
-                        case 3: src = (const T *)a.v + b2 * a.v_bs + row * a.v_rs; break;
-                        default: src = (const T *)a.out + b2 * a.o_bs + row * a.o_rs; break;
-                    }
-                    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(src + (int64_t)h2 * D + (rem % LPR) * 64));
-                }
-                // ... and the left children of levels 1..5 inside that tile (31 rows of K and of V)
-                for (int i = tid; i < 2 * 31 * LPR; i += 256) {
-                    const int which = i / (31 * LPR), rem = i % (31 * LPR);
-                    const int f = rem / LPR;
-                    const int l = 5 - (31 - __clz(31 - f));                 // 16, 8, 4, 2, 1 nodes of levels 1..5
-                    const int64_t row = level_base(N, l) + ((tile2 * kTile) >> l) + 2 * (f - (32 - (64 >> l)));
-                    const T *src = which ? (const T *)a.v + b2 * a.v_bs + row * a.v_rs : (const T *)a.k + b2 * a.k_bs + row * a.k_rs;
-                    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(src + (int64_t)h2 * D + (rem % LPR) * 64));
-                }
-            }
         }
 
         // delta = rowsum(dOut * Out) and base-2 log-sum-exp per staged query row; all global loads are issued
@@ -742,12 +706,6 @@ int hsa_span_attn_bwd_tc8(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, cons
     a.dk_bs = dK.batch_stride; a.dk_rs = dK.row_stride; a.dv_bs = dV.batch_stride; a.dv_rs = dV.row_stride;
     a.N = N; a.L = ilog2((unsigned)N); a.H = H; a.R = radius < N ? radius : N;
     a.ntb = p.ntb; a.tree_rows = p.tree_rows;
-    {
-        int dev = 0, sms = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        a.pf_dist = (sms > 0 ? sms : 148) * 3 / 4;
-    }
     a.kb_off = p.kb_off; a.vt_off = p.vt_off; a.kt_off = p.kt_off; a.q_off = p.q_off; a.go_off = p.go_off;
     a.stat_off = p.stat_off; a.tiles_off = p.tiles_off; a.ttiles_off = p.ttiles_off; a.persist_off = p.persist_off;
     a.mbar_off = p.mbar_off;
