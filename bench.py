@@ -2,6 +2,7 @@
 """Benchmark of the hierarchical sparse attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+                    [--only fwd|bwd|parents|parent_tree|lm|reference_triton]
 
 One step = one pass of the span-attention forward over one batch of synthetic Q/K/V (the layer
 shape of the N=4096 headline: bf16, H=16, head_dim=128, radius 16, causal, batch 32 per GPU).
@@ -9,22 +10,29 @@ Under torchrun every rank runs its own batch shard (weak scaling, no data-path c
 time is the max over ranks of CUDA-event time between barriers.  Prints ONE JSON line on rank 0.
 
 Keys beyond the base contract:
-  roofline      the dominant kernel against the measured HBM copy bandwidth (MEASURED_PEAKS.json)
+  roofline      the dominant kernel against the measured HBM copy bandwidth (MEASURED_PEAKS.json):
+                `achieved` / `frac` are EFFECTIVE bandwidth (algorithmic bytes / kernel time),
+                `frac_dram` is measured DRAM traffic (ncu, scaled by batch) / kernel time / peak
   cpu_baseline  the CPU oracle (a port of the reference's eager layer math) timed on this box's
                 host cores on a bounded sample of the same workload
   e2e           same metric through the public Python API with host (pinned) inputs copied in
                 and the result copied out inside the timed region
-  extras        parent-node build and forward+backward figures on the same shape
+  extras        backward, parent-node build, a multi-second loop of the headline kernel with the
+                sampled SM clock, the LM training step (8x4096 and 8x2048 per GPU; tensor roofline,
+                exposed all-reduce time) and the reference's Triton package timed on the same GPU
 `--impl reference` times the CPU oracle instead (the reference has no GPU-independent compiled
 path; its own implementation of this layer on a CPU is eager PyTorch, which the oracle restates).
+`--only X` runs just one kernel loop on the chosen workload and prints a short JSON line: the
+command profiler captures are taken from.
 """
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
-import math
 import os
 import statistics
+import subprocess
 import sys
 import threading
 import time
@@ -39,34 +47,49 @@ WORKLOADS = {
     # name: (B per GPU, N, H, D, R, causal, dtype)
     "layer_n4096": (32, 4096, 16, 128, 16, True, torch.bfloat16),
     "layer_n4096_small": (4, 4096, 16, 128, 16, True, torch.bfloat16),     # for profiler captures
-    "config2": (16, 512, 8, 64, 8, True, torch.bfloat16),
+    "layer_n4096_b8": (8, 4096, 16, 128, 16, True, torch.bfloat16),        # for profiler captures
+    "b16_h8_n512": (16, 512, 8, 64, 8, True, torch.bfloat16),
 }
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS_SUSTAINED = 1400.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel, measured with ncu on
-# `--workload layer_n4096_small` (profiles/), scaled by batch (traffic is proportional to batch).
-NCU_TRAFFIC_BYTES_PER_BATCH_ELEM = {"layer_n4096": 317.2e6 / 4, "layer_n4096_small": 317.2e6 / 4}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of span_fwd_tc128_kernel at batch 4
+# (`--workload layer_n4096_small`, ncu --set full): 316.6 MB.  Traffic is proportional to batch, because
+# every (batch, head, tile) thread block reads its own rows.
+NCU_TRAFFIC_BYTES_PER_BATCH_ELEM = 316.6e6 / 4
+NCU_TRAFFIC_WORKLOADS = ("layer_n4096", "layer_n4096_small", "layer_n4096_b8")
+
+REF_TRITON_DIR = os.path.join(ROOT, "baseline", "_ref", "hierarchical_attention")
 
 
 def measured_peaks():
+    """(HBM GB/s, sustained bf16 TFLOP/s, "measured" | "fallback")."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as fh:
             d = json.load(fh)
-        return float(d["hbm_gbs"]), "measured"
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", FALLBACK_BF16_TFLOPS_SUSTAINED)), "measured"
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback"
+        return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS_SUSTAINED, "fallback"
 
 
 def algorithmic_bytes_fwd(B, N, H, D, esize, causal):
-    """Rows that must cross HBM once: Q, Out, and the attended K/V rows (module docstring of DESIGN.md)."""
+    """Rows that must cross HBM once: Q, Out, and the attended K/V rows (causal: leaves + left children)."""
     row = H * D * esize
     return B * row * ((5 * N - 2) if causal else (6 * N - 4))
 
 
 def algorithmic_bytes_bwd(B, N, H, D, esize, causal):
+    """Read Q, Out, dOut and the attended K/V rows; write dQ and every row of dK, dV."""
     row = H * D * esize
     return B * row * ((11 * N - 4) if causal else (12 * N - 6))
+
+
+def lm_flops_per_token(d=512, d_ff=2048, layers=6, vocab=50257):
+    """Forward matrix-multiply flops per token of the LM: per layer 14 d x d projections (bottom-up: Q/K/V of the
+    parents, K/V of the leaves, K/V of the refreshed parents, out_proj_y; top-down: Q, K/V of leaves and parents,
+    out_proj_x) and the feed-forward pair, plus the LM head."""
+    return layers * (14 * 2 * d * d + 4 * d * d_ff) + 2 * d * vocab
 
 
 class ClockSampler:
@@ -166,6 +189,15 @@ def time_cuda(fn, steps, warmup, barrier):
     return e0.elapsed_time(e1)
 
 
+def max_over_ranks(ms, device, use_dist):
+    if not use_dist:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def oracle_tokens_per_s(workload, budget_s: float, threads: int):
     """CPU oracle on a bounded sample of the workload's leaves (all heads, one batch entry)."""
     from oracle import hsa_oracle as orc
@@ -217,30 +249,33 @@ def run_reference(args):
     emit(line)
 
 
-LM_CONFIGS = {
-    # BASELINE configs 3 and 4: 6 layers, d_model 512, 8 heads, FFN 2048, window 16, vocab 50257, bf16
-    "lm_8x2048": dict(batch=8, seq=2048), "lm_8x4096": dict(batch=8, seq=4096),
-}
+# The LM of the training-step metric: 6 layers, d_model 512, 8 heads, FFN 2048, window 16, vocabulary 50257, bf16
+# autocast; batch x sequence per GPU.
+LM_CONFIGS = {"lm_8x2048": dict(batch=8, seq=2048), "lm_8x4096": dict(batch=8, seq=4096)}
+LM_VOCAB = 50257
 
 
-def run_lm(args, device, world, rank, barrier, use_dist, strong=False):
+def run_lm(args, device, world, rank, barrier, use_dist, name, strong=False, allreduce=True, attention_cls=None,
+           graph=True, steps=None):
     """Training step (forward, loss, backward, gradient all-reduce, clip, AdamW) of the hierarchical LM
     on Zipf(1.1) token ids.  Per-GPU batch fixed (weak scaling) unless `strong`, which splits the config's
-    batch over the ranks (global batch fixed).  Returns whole-job tokens/s."""
+    batch over the ranks (global batch fixed).  `allreduce=False` leaves the collective out (to see what it
+    costs on the same ranks).  Returns whole-job tokens/s and the step's share of the tensor roofline."""
     import torch.distributed as dist
     from sparseattention_b200.dp import BucketedGradAverager
     from sparseattention_b200.lm import TransformerLM, lm_loss, zipf_tokens
+    from sparseattention_b200.train import GraphedStep
 
-    cfg = dict(LM_CONFIGS[args.lm])
+    cfg = dict(LM_CONFIGS[name])
     if strong:
         cfg["batch"] //= world
-    vocab = 50257
     torch.manual_seed(0)
-    model = TransformerLM(vocab, 512, 8, 2048, 6, dropout=0.1, window_size=16).to(device)
-    avg = BucketedGradAverager(model.parameters())
-    use_graph = not args.no_cuda_graph
+    kwargs = {} if attention_cls is None else {"attention_cls": attention_cls}
+    model = TransformerLM(LM_VOCAB, 512, 8, 2048, 6, dropout=0.1, window_size=16, **kwargs).to(device)
+    avg = BucketedGradAverager(model.parameters(), communicate=allreduce)
+    use_graph = graph and not args.no_cuda_graph
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True, capturable=use_graph)
-    host_tokens = zipf_tokens(cfg["batch"], cfg["seq"] + 1, vocab, seed=4321 + rank).pin_memory()
+    host_tokens = zipf_tokens(cfg["batch"], cfg["seq"] + 1, LM_VOCAB, seed=4321 + rank).pin_memory()
     tokens = torch.empty(host_tokens.shape, dtype=host_tokens.dtype, device=device)
     loss_buf = torch.zeros((), device=device)
     losses = []
@@ -256,57 +291,253 @@ def run_lm(args, device, world, rank, barrier, use_dist, strong=False):
         opt.step()
         loss_buf.copy_(loss.detach())
 
-    # The whole step is captured once in a CUDA graph and replayed (the launches of the ~2500 small kernels of
-    # a step otherwise cost more host time than the GPU needs); eager launching is used if capture is refused.
-    graph = None
-    if use_graph:
-        try:
-            side = torch.cuda.Stream(device)
-            side.wait_stream(torch.cuda.current_stream(device))
-            with torch.cuda.stream(side):
-                for _ in range(3):
-                    body()
-            torch.cuda.current_stream(device).wait_stream(side)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                body()
-        except Exception as exc:                              # pragma: no cover - depends on the runtime
-            graph = None
-            graph_error = f"{type(exc).__name__}: {exc}"[:200]
-            torch.cuda.synchronize()
+    runner = GraphedStep(body, device, enabled=use_graph)
     if use_dist:                                              # every rank must take the same path
-        flag = torch.tensor([1 if graph is not None else 0], device=device)
+        flag = torch.tensor([1 if runner.captured else 0], device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) == 0:
-            graph = None
+            runner.drop_graph()
 
     def step():
-        if graph is not None:
-            graph.replay()
-        else:
-            body()
+        runner()
         losses.append(loss_buf.clone())
 
-    steps = max(3, min(args.steps, 10))
-    ms = time_cuda(step, steps, 3, barrier)
-    if use_dist:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms /= steps
+    steps = steps or max(3, min(args.steps, 10))
+    ms = max_over_ranks(time_cuda(step, steps, 3, barrier), device, use_dist) / steps
     tok = cfg["batch"] * cfg["seq"] * world
     nparams = sum(p.numel() for p in model.parameters())
-    out = {"config": args.lm, "scaling": "strong" if strong else "weak", "tokens_per_s": tok / (ms * 1e-3),
+    _, tf_peak, peak_kind = measured_peaks()
+    flops_step = 3 * lm_flops_per_token() * cfg["batch"] * cfg["seq"]        # per GPU: forward + backward (2x)
+    tflops = flops_step / (ms * 1e-3) / 1e12
+    out = {"config": name, "scaling": "strong" if strong else "weak", "tokens_per_s": tok / (ms * 1e-3),
            "ms_per_step": ms, "steps": steps,
            "global_batch": cfg["batch"] * world, "seq_len": cfg["seq"], "params": nparams,
-           "allreduce_bytes_per_step": avg.bytes_per_step() if world > 1 else 0,
+           "allreduce_bytes_per_step": avg.bytes_per_step() if (world > 1 and allreduce) else 0,
            "loss_first": float(losses[0]), "loss_last": float(losses[-1]),
            "step": "fwd + label-smoothed CE + bwd + NCCL grad all-reduce + clip + AdamW, bf16 autocast",
-           "cuda_graph": graph is not None}
-    del model, opt, avg, graph
+           "cuda_graph": runner.captured,
+           "roofline": {"bound": "tensor", "achieved": tflops, "peak": tf_peak, "unit": "TFLOP/s",
+                        "frac": tflops / tf_peak, "peak_source": peak_kind + " (sustained bf16 matmul)",
+                        "flops_per_step_per_gpu": flops_step,
+                        "flops": "3 x forward matrix-multiply flops (120.7 MFLOP per token)"}}
+    del model, opt, avg, runner
     torch.cuda.empty_cache()
     return out
+
+
+def sizes_of(N):
+    sizes, n = [], N
+    while n > 1:
+        n //= 2
+        sizes.append(n)
+    return sizes
+
+
+def kernel_loops(workload, device):
+    """Closures that run one kernel (or one kernel per tree level) of the hot path on `workload`:
+    {"fwd", "bwd", "parents", "parents_bwd"} -> (callable, algorithmic bytes, launches per call)."""
+    import sparseattention_b200 as hsa
+    from sparseattention_b200 import _lib
+    from sparseattention_b200.ops import functional as F
+
+    B, N, H, D, R, causal, dtype = WORKLOADS[workload]
+    esize = torch.finfo(dtype).bits // 8
+    lib = _lib.load()
+    state = {}
+
+    def qkv():
+        if "qkv" not in state:
+            state["qkv"] = make_inputs(B, N, H, D, dtype, 1234, device)
+        return state["qkv"]
+
+    def fwd():
+        Q, K, V = qkv()
+        F.span_attention_forward(Q, K, V, R, causal, need_lse=False)
+
+    def bwd():
+        Q, K, V = qkv()
+        if "bwd" not in state:
+            out, lse = F.span_attention_forward(Q, K, V, R, causal, need_lse=True)
+            state["bwd"] = (out, lse, torch.randn_like(out))
+        out, lse, go = state["bwd"]
+        F.span_attention_backward(Q, K, V, out, lse, go, R, causal)
+
+    sizes = sizes_of(N)
+
+    def parent_tensors():
+        if "par" not in state:
+            gen = torch.Generator(device=device).manual_seed(7)
+            Pq, Pk, Pv = (torch.randn(B, N - 1, H, D, generator=gen, device=device, dtype=dtype) for _ in range(3))
+            Ck, Cv = (torch.randn(B, N, H, D, generator=gen, device=device, dtype=dtype) for _ in range(2))
+            state["par"] = (Pq, Pk, Pv, Ck, Cv)
+        return state["par"]
+
+    def parents():
+        Pq, Pk, Pv, Ck, Cv = parent_tensors()
+        qs, ks, vs = (torch.split(t, sizes, dim=1) for t in (Pq, Pk, Pv))
+        with torch.no_grad():
+            for lvl, P in enumerate(sizes):
+                hsa.build_parent_nodes(qs[lvl], ks[lvl], vs[lvl], Ck[:, :2 * P], Cv[:, :2 * P])
+
+    def parents_bwd():
+        Pq, Pk, Pv, Ck, Cv = parent_tensors()
+        if "pgrads" not in state:
+            state["pgrads"] = ([torch.empty_like(t) for t in (Pq, Pk, Pv, Ck, Cv)], torch.randn_like(Pq))
+        grads, gout = state["pgrads"]
+        qs, ks, vs = (torch.split(t, sizes, dim=1) for t in (Pq, Pk, Pv))
+        gq, gk, gv = (torch.split(t, sizes, dim=1) for t in grads[:3])
+        gos = torch.split(gout, sizes, dim=1)
+        dt = _lib.dtype_code(Pq)
+        for lvl, P in enumerate(sizes):
+            views = [_lib.rows_view(t) for t in (gos[lvl], qs[lvl], ks[lvl], vs[lvl], Ck[:, :2 * P], Cv[:, :2 * P],
+                                                 gq[lvl], gk[lvl], gv[lvl], grads[3][:, :2 * P], grads[4][:, :2 * P])]
+            _lib.check(lib.hsa_parent_nodes_bwd(*views, B, P, H, D, dt, _lib.stream_ptr(device)), "hsa_parent_nodes_bwd")
+
+    row = B * H * D * esize
+    return {
+        "fwd": (fwd, algorithmic_bytes_fwd(B, N, H, D, esize, causal), 1),
+        "bwd": (bwd, algorithmic_bytes_bwd(B, N, H, D, esize, causal), 2),
+        "parents": (parents, row * 8 * (N - 1), len(sizes)),
+        "parents_bwd": (parents_bwd, row * 15 * (N - 1), len(sizes)),
+    }, state
+
+
+def run_only(args):
+    """One kernel loop on the chosen workload (what profiler captures are taken from)."""
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    if args.only == "reference_triton":
+        emit(reference_triton_child(args, device))
+        return
+    if args.only == "lm":
+        out = run_lm(args, device, 1, 0, lambda: None, False, args.lm, graph=not args.no_cuda_graph)
+        emit({"only": "lm", **out})
+        return
+    loops, _ = kernel_loops(args.workload, device)
+    fn, alg, launches = loops[args.only]
+    ms = time_cuda(fn, args.steps, args.warmup, lambda: None) / args.steps
+    peak, _, kind = measured_peaks()
+    emit({"only": args.only, "workload": args.workload, "ms": ms, "launches_per_call": launches,
+          "achieved_gbs": alg / (ms * 1e-3) / 1e9, "frac_of_hbm": alg / (ms * 1e-3) / 1e9 / peak, "peak_source": kind})
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The reference project's own Triton package, unmodified, on this GPU (a copy of its `hierarchical_attention`
+# directory under baseline/_ref/, made by __graft_entry__.build() where the reference checkout is mounted).
+# Runs in a child process with a time limit: a failure of Triton's JIT on this GPU, or a fault in code this
+# repository does not control, must not take the benchmark with it.
+# ---------------------------------------------------------------------------------------------------------------
+def load_reference_package():
+    init = os.path.join(REF_TRITON_DIR, "__init__.py")
+    if not os.path.exists(init):
+        return None
+    spec = importlib.util.spec_from_file_location("reference_hierarchical_attention", init,
+                                                  submodule_search_locations=[REF_TRITON_DIR])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["reference_hierarchical_attention"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def reference_triton_child(args, device):
+    ref = load_reference_package()
+    if ref is None:
+        return {"unavailable": "baseline/_ref/hierarchical_attention is not there (reference checkout absent at build time)"}
+    import sparseattention_b200 as hsa
+    out = {"package": "reference hierarchical_attention (Triton JIT), unmodified", "triton": None}
+    try:
+        import triton
+        out["triton"] = triton.__version__
+    except Exception as exc:
+        return {"unavailable": f"triton does not import: {exc}"[:200]}
+    B, N, H, D, R, causal, dtype = WORKLOADS[args.workload]
+    nsteps, nwarm = 10, 3
+
+    def timed(fn):
+        return time_cuda(fn, nsteps, nwarm, lambda: None) / nsteps
+
+    def section(name, fn):
+        try:
+            out[name] = fn()
+        except Exception as exc:                      # JIT failure, unsupported shape, out of memory ...
+            out[name] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+            torch.cuda.synchronize()
+
+    # ---- op level: span attention forward and forward+backward on the benchmark's Q/K/V
+    def span_ops():
+        Q, K, V = make_inputs(B, N, H, D, dtype, 1234, device)
+        res = {"shape": {"B": B, "N": N, "H": H, "D": D, "radius": R, "causal": causal, "dtype": "bf16"}}
+        for label, pkg in (("reference", ref), ("ours", hsa)):
+            t = pkg.build_tree_topology(N, is_causal=causal, device=device)
+            mask = t["forward_mask"] if causal else None
+            with torch.no_grad():
+                fwd_ms = timed(lambda: pkg.hierarchical_attention(Q, K, V, t["forward_idx"], t["backward_gather"], mask, R))
+            q, k, v = (x.clone().requires_grad_() for x in (Q, K, V))
+            go = torch.randn_like(Q)
+
+            def fb():
+                o = pkg.hierarchical_attention(q, k, v, t["forward_idx"], t["backward_gather"], mask, R)
+                o.backward(go)
+                q.grad = k.grad = v.grad = None
+            res[label] = {"fwd_ms": fwd_ms, "fwd_tokens_per_s": B * N / (fwd_ms * 1e-3), "fwd_bwd_ms": timed(fb)}
+            del q, k, v, go
+            torch.cuda.empty_cache()
+        res["speedup_fwd"] = res["reference"]["fwd_ms"] / res["ours"]["fwd_ms"]
+        res["speedup_fwd_bwd"] = res["reference"]["fwd_bwd_ms"] / res["ours"]["fwd_bwd_ms"]
+        return res
+
+    # ---- module level: cross_update_Y forward+backward at the shape the reference's own benchmark uses
+    # (hierarchical_attention_project/Hierarchical_Attention_Triton_Test.py:504: B 32, N 4096, 8 heads of 64)
+    def bottom_up():
+        Bm, Nm, Hm, Dm = 32, 4096, 8, 64
+        dim = Hm * Dm
+        res = {"shape": {"B": Bm, "N": Nm, "H": Hm, "D": Dm, "dtype": "bf16"}}
+        x = torch.randn(Bm, Nm, dim, device=device, dtype=dtype, requires_grad=True)
+        y = torch.randn(Bm, Nm - 1, dim, device=device, dtype=dtype, requires_grad=True)
+        dout = torch.randn(Bm, Nm - 1, dim, device=device, dtype=dtype)
+        for label, pkg in (("reference", ref), ("ours", hsa)):
+            torch.manual_seed(0)
+            m = pkg.HierarchicalAttention(dim, Hm, dropout=0.0).to(device).to(dtype).eval()
+
+            def fb():
+                o = m.cross_update_Y(x, y)
+                o.backward(dout)
+                m.zero_grad(); x.grad = None; y.grad = None
+            res[label] = {"fwd_bwd_ms": timed(fb)}
+            del m
+        res["speedup"] = res["reference"]["fwd_bwd_ms"] / res["ours"]["fwd_bwd_ms"]
+        return res
+
+    # ---- model level: one LM training step with the reference's module injected, both launched eagerly
+    def lm_step():
+        res = {"config": args.lm, "launch": "eager (no CUDA graph) for both"}
+        for label, cls in (("reference", ref.HierarchicalAttention), ("ours", None)):
+            r = run_lm(args, device, 1, 0, lambda: None, False, args.lm, attention_cls=cls, graph=False, steps=5)
+            res[label] = {"ms_per_step": r["ms_per_step"], "tokens_per_s": r["tokens_per_s"], "loss_last": r["loss_last"]}
+        res["speedup"] = res["reference"]["ms_per_step"] / res["ours"]["ms_per_step"]
+        return res
+
+    section("span_attention", span_ops)
+    section("cross_update_Y", bottom_up)
+    section("lm_train_step", lm_step)
+    return out
+
+
+def reference_triton_parent(args):
+    """Run `--only reference_triton` in a child with a time limit and return its JSON (or why there is none)."""
+    if not os.path.exists(os.path.join(REF_TRITON_DIR, "__init__.py")):
+        return {"unavailable": "baseline/_ref/hierarchical_attention is not there (reference checkout absent at build time)"}
+    cmd = [sys.executable, os.path.abspath(__file__), "--only", "reference_triton", "--workload", args.workload, "--lm", args.lm]
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=args.reference_triton_seconds)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"no result within {args.reference_triton_seconds} s (child process stopped)"}
+    for ln in reversed(res.stdout.strip().splitlines()):
+        try:
+            return json.loads(ln)
+        except Exception:
+            continue
+    return {"unavailable": f"child exited {res.returncode}: {res.stderr.strip()[-300:]}"}
 
 
 def run_ours(args):
@@ -337,7 +568,6 @@ def run_ours(args):
     _lib.load()
     Qh, Kh, Vh = make_inputs(B, N, H, D, dtype, 1234 + rank, None, pinned=True)
     Q, K, V = (t.to(device) for t in (Qh, Kh, Vh))
-    tables = hsa.build_tree_topology(N, causal, device=device)
     footprint = sum(t.numel() * t.element_size() for t in (Q, K, V)) + Q.numel() * esize
 
     # ---- device-resident: raw forward (inference form: no LSE) -------------------------------
@@ -346,17 +576,35 @@ def run_ours(args):
 
     with ClockSampler(local) as clk:
         ms = time_cuda(step, args.steps, args.warmup, barrier)
-    if use_dist:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = max_over_ranks(ms, device, use_dist)
     ms_step = ms / args.steps
     tokens_step = B * N * world
     value = tokens_step / (ms_step * 1e-3)
-    peak, peak_kind = measured_peaks()
+    peak, tf_peak, peak_kind = measured_peaks()
     alg = algorithmic_bytes_fwd(B, N, H, D, esize, causal)
     achieved = alg / (ms_step * 1e-3) / 1e9
-    traffic = NCU_TRAFFIC_BYTES_PER_BATCH_ELEM.get(args.workload)
+    traffic = NCU_TRAFFIC_BYTES_PER_BATCH_ELEM * B if args.workload in NCU_TRAFFIC_WORKLOADS else None
+
+    extras = {}
+    # ---- the same kernel back to back for >= 2 s, with the SM clock sampled while it runs ------------
+    if world == 1 and not args.no_extras:
+        per_round = max(1, int(200.0 / ms_step))                      # ~0.2 s of launches between host checks
+        with ClockSampler(local, period_s=0.05) as sclk:
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t_start, launches = time.perf_counter(), 0
+            e0.record()
+            while time.perf_counter() - t_start < args.sustained_seconds:
+                for _ in range(per_round):
+                    step()
+                launches += per_round
+                torch.cuda.synchronize()
+            e1.record()
+            torch.cuda.synchronize()
+        sms = e0.elapsed_time(e1) / launches
+        extras["fwd_sustained"] = {"seconds": e0.elapsed_time(e1) / 1e3, "launches": launches, "ms": sms,
+                                   "tokens_per_s": B * N / (sms * 1e-3), "achieved_gbs": alg / (sms * 1e-3) / 1e9,
+                                   "frac_of_hbm": alg / (sms * 1e-3) / 1e9 / peak, "clocks": sclk.summary()}
 
     # ---- end to end through the public API with host buffers -----------------------------------
     out_host = torch.empty((B, N, H, D), dtype=dtype).pin_memory()
@@ -366,77 +614,48 @@ def run_ours(args):
         # public host-side entry point: pinned inputs in, pinned result out, copies overlapped with compute
         F.hierarchical_attention_from_host(Qh, Kh, Vh, R, causal, out=out_host, device=device)
 
-    e2e_ms = time_cuda(e2e_step, e2e_steps, 1, barrier)
-    if use_dist:
-        t = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks(time_cuda(e2e_step, e2e_steps, 1, barrier), device, use_dist)
     e2e_value = tokens_step / (e2e_ms / e2e_steps * 1e-3)
-    h2d = sum(t.numel() * t.element_size() for t in (Qh, Kh, Vh))
+    h2d = F.host_entry_h2d_bytes(B, N, H, D, esize, causal)
     d2h = out_host.numel() * out_host.element_size()
 
-    # ---- extras: training forward (+LSE), backward, parent build on the same shape -------------
-    extras = {}
+    # ---- extras: backward and parent build on the same shape -------------
     launches_per_step = 1
+    del Q, K, V
+    torch.cuda.empty_cache()
     if rank == 0 and not args.no_extras:
-        out, lse = F.span_attention_forward(Q, K, V, R, causal, need_lse=True)
-        go = torch.randn_like(out)
+        loops, state = kernel_loops(args.workload, device)
         bsteps = max(3, min(args.steps, 20))
-        bms = time_cuda(lambda: F.span_attention_backward(Q, K, V, out, lse, go, R, causal), bsteps, 3,
-                        lambda: None) / bsteps
-        balg = algorithmic_bytes_bwd(B, N, H, D, esize, causal)
-        extras["span_bwd"] = {"ms": bms, "tokens_per_s": B * N / (bms * 1e-3), "achieved_gbs": balg / (bms * 1e-3) / 1e9,
-                              "frac_of_hbm": balg / (bms * 1e-3) / 1e9 / peak}
-        del out, lse, go
-        # parent build: all levels, op level (8 rows per parent forward)
-        sizes = []
-        n = N
-        while n > 1:
-            n //= 2
-            sizes.append(n)
-        gen = torch.Generator(device=device).manual_seed(7)
-        Pq, Pk, Pv = (torch.randn(B, N - 1, H, D, generator=gen, device=device, dtype=dtype) for _ in range(3))
-        Ck, Cv = (torch.randn(B, N, H, D, generator=gen, device=device, dtype=dtype) for _ in range(2))
-        qs, ks, vs = (torch.split(t, sizes, dim=1) for t in (Pq, Pk, Pv))
-
-        def parents():
-            kc, vc = Ck, Cv
-            for lvl, P in enumerate(sizes):
-                hsa.build_parent_nodes(qs[lvl], ks[lvl], vs[lvl], kc[:, :2 * P], vc[:, :2 * P])
-
-        with torch.no_grad():
-            pms = time_cuda(parents, bsteps, 3, lambda: None) / bsteps
-        palg = B * H * D * esize * 8 * (N - 1)
-        extras["parent_build_fwd_all_levels"] = {
-            "ms": pms, "launches": len(sizes), "achieved_gbs": palg / (pms * 1e-3) / 1e9,
-            "frac_of_hbm": palg / (pms * 1e-3) / 1e9 / peak}
-        # backward of every level through the C ABI directly (15 rows per parent)
-        lib = _lib.load()
-        grads = [torch.empty_like(t) for t in (Pq, Pk, Pv, Ck, Cv)]
-        gq, gk, gv = (torch.split(t, sizes, dim=1) for t in grads[:3])
-        gout = torch.randn_like(Pq)
-        gos = torch.split(gout, sizes, dim=1)
-        dt = _lib.dtype_code(Pq)
-
-        def parents_bwd():
-            for lvl, P in enumerate(sizes):
-                views = [_lib.rows_view(t) for t in (gos[lvl], qs[lvl], ks[lvl], vs[lvl], Ck[:, :2 * P], Cv[:, :2 * P],
-                                                     gq[lvl], gk[lvl], gv[lvl], grads[3][:, :2 * P], grads[4][:, :2 * P])]
-                _lib.check(lib.hsa_parent_nodes_bwd(*views, B, P, H, D, dt, _lib.stream_ptr(device)), "hsa_parent_nodes_bwd")
-
-        pbms = time_cuda(parents_bwd, bsteps, 3, lambda: None) / bsteps
-        pbalg = B * H * D * esize * 15 * (N - 1)
-        extras["parent_build_bwd_all_levels"] = {
-            "ms": pbms, "launches": len(sizes), "achieved_gbs": pbalg / (pbms * 1e-3) / 1e9,
-            "frac_of_hbm": pbalg / (pbms * 1e-3) / 1e9 / peak}
-        del Pq, Pk, Pv, Ck, Cv, grads, gout
+        for key, name in (("bwd", "span_bwd"), ("parents", "parent_build_fwd_all_levels"),
+                          ("parents_bwd", "parent_build_bwd_all_levels")):
+            fn, kalg, launches = loops[key]
+            kms = time_cuda(fn, bsteps, 3, lambda: None) / bsteps
+            extras[name] = {"ms": kms, "launches": launches, "achieved_gbs": kalg / (kms * 1e-3) / 1e9,
+                            "frac_of_hbm": kalg / (kms * 1e-3) / 1e9 / peak}
+            if key == "bwd":
+                extras[name]["tokens_per_s"] = B * N / (kms * 1e-3)
+        state.clear()
+        del loops
+        torch.cuda.empty_cache()
 
     # ---- the model that calls the layer: data-parallel LM training step (all ranks) ---------------
     if not args.no_lm:
-        extras["lm_train"] = run_lm(args, device, world, rank, barrier, use_dist)
-        if world > 1 and LM_CONFIGS[args.lm]["batch"] % world == 0:
-            # secondary line: the same global batch as one GPU, split over the ranks
-            extras["lm_train_strong"] = run_lm(args, device, world, rank, barrier, use_dist, strong=True)
+        lm = run_lm(args, device, world, rank, barrier, use_dist, args.lm)
+        extras["lm_train"] = lm
+        if world > 1:
+            # the same step on the same ranks without the collective: the difference is what the all-reduce
+            # adds to the step after overlap with the backward
+            quiet = run_lm(args, device, world, rank, barrier, use_dist, args.lm, allreduce=False)
+            lm["ms_per_step_without_allreduce"] = quiet["ms_per_step"]
+            lm["allreduce_exposed_ms"] = lm["ms_per_step"] - quiet["ms_per_step"]
+            if LM_CONFIGS[args.lm]["batch"] % world == 0:
+                # secondary line: the same global batch as one GPU, split over the ranks
+                extras["lm_train_strong"] = run_lm(args, device, world, rank, barrier, use_dist, args.lm, strong=True)
+        other = "lm_8x2048" if args.lm != "lm_8x2048" else "lm_8x4096"
+        extras["lm_train_" + other[3:]] = run_lm(args, device, world, rank, barrier, use_dist, other)
+        extras["lm_scaling"] = {"n_gpus": world, "tokens_per_s": lm["tokens_per_s"], "ms_per_step": lm["ms_per_step"],
+                                "allreduce_exposed_ms": lm.get("allreduce_exposed_ms", 0.0),
+                                "frac_of_tensor_roofline": lm["roofline"]["frac"]}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -445,6 +664,8 @@ def run_ours(args):
         cpu = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
                "sample": f"{n} leaves x {H} heads of one batch entry, {s:.1f} s "
                          f"(eager PyTorch CPU oracle, {cores} threads)"}
+    if rank == 0 and world == 1 and not args.no_extras and not args.no_reference_triton:
+        extras["reference_triton"] = reference_triton_parent(args)
 
     if rank == 0:
         line = {
@@ -458,7 +679,10 @@ def run_ours(args):
                        "l2": f"inputs+outputs {footprint / 1e6:.0f} MB per GPU exceed the 126 MB L2; no flush"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": peak_kind,
-                         "traffic": None if traffic is None else traffic * B,
+                         "achieved_kind": "effective bandwidth: algorithmic bytes / kernel time",
+                         "traffic": traffic,
+                         "frac_dram": None if traffic is None else traffic / (ms_step * 1e-3) / 1e9 / peak,
+                         "traffic_source": "ncu dram bytes of span_fwd_tc128_kernel at batch 4, scaled by batch",
                          "algorithmic_bytes_per_launch": alg, "kernel_ms": ms_step},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
@@ -474,11 +698,11 @@ def run_ours(args):
 
 
 def run_sweep(args):
-    """BASELINE config 5: forward-only bf16 sweep over N and batch (H=16, D=128, causal, radius 16 and 32).
+    """Forward-only bf16 sweep over N and batch (H=16, D=128, causal, radius 16 and 32).
     Prints a markdown table: achieved algorithmic GB/s and fraction of the measured HBM copy bandwidth."""
     from sparseattention_b200.ops import functional as F
     torch.cuda.set_device(0)
-    peak, kind = measured_peaks()
+    peak, _, kind = measured_peaks()
     H, D = 16, 128
     print(f"| N | B | radius | ms | tokens/s | GB/s (algorithmic) | of {kind} {peak:.0f} GB/s | footprint MB |")
     print("|---|---|---|---|---|---|---|---|")
@@ -515,10 +739,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="layer_n4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--only", default=None, choices=["fwd", "bwd", "parents", "parents_bwd", "lm", "reference_triton"],
+                    help="run one kernel loop (or the LM step, or the reference's Triton package) and print a short JSON line")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--sustained-seconds", type=float, default=2.5)
+    ap.add_argument("--reference-triton-seconds", type=int, default=420)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-lm", action="store_true")
+    ap.add_argument("--no-reference-triton", action="store_true")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch the LM step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--lm", default="lm_8x4096", choices=sorted(LM_CONFIGS))
     ap.add_argument("--sweep", action="store_true", help="print the forward sweep over N and batch instead of the JSON line")
@@ -533,7 +762,9 @@ def main():
     _JSON_OUT = os.fdopen(os.dup(1), "w")
     os.dup2(2, 1)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.only is not None:
+        run_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

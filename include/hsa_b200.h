@@ -118,12 +118,25 @@ int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *L
                       int H, int D, int radius, int causal, int dtype, int algo, void *stream);
 
 /*
- * Diagnostic with no reference counterpart: the TMA-staged kernels (128-leaf forward, 8-warp backward) wait
- * for their bulk copies on mbarriers with a time limit (about a second); a CTA whose wait runs out counts
- * itself, skips its tile and returns.  *count receives the number of such CTAs on the current device since
- * the library was loaded (0 in any healthy run).  Synchronises with the device (cudaMemcpyFromSymbol).
+ * Diagnostic with no reference counterpart.  The TMA-staged kernels (128-leaf and 64-leaf forward, 8-warp
+ * backward) wait for their bulk copies on mbarriers with a time limit (about a second).  A CTA whose wait runs
+ * out counts itself, writes NaN instead of results (forward: its Out and LSE rows; backward: its dQ rows and its
+ * partial rows of the upper levels, which reach dK / dV) and returns; the launch still reports success, because
+ * the library never synchronises.  *count receives the number of such CTAs on the current device since the
+ * library was loaded: 0 in any healthy run.  A caller that wants certainty checks it after synchronising (the
+ * Python binding does so after every span-attention call when HSA_B200_DEBUG=1).  This call synchronises with
+ * the device (cudaMemcpyFromSymbol).
  */
 int hsa_span_attn_fwd_wait_expired(unsigned int *count);
+
+/*
+ * Test hook with no reference counterpart, for the give-up path described above: later launches of the
+ * TMA-staged kernels wait at most `limit_cycles` clock cycles, and the first barrier of every CTA expects
+ * `extra_tx_bytes` more bytes than its copies deliver.  With extra_tx_bytes > 0 every copy still completes but
+ * that barrier never does, so each CTA gives up once the limit has passed, with nothing left in flight.
+ * (2000000000, 0) restores normal operation.  Host-side state only; nothing is launched.
+ */
+int hsa_debug_wait_test(long long limit_cycles, unsigned int extra_tx_bytes);
 
 /*
  * Span attention backward.  Replaces HierarchicalAttentionFunc.backward
@@ -146,7 +159,9 @@ int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const fl
  * label_smoothing=0.1) applied to the [B*N, vocab] logits
  * (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.py:514, 562-572).
  *   logits  [M, >= V] with `row_stride` elements between rows; only columns [0, V) are classes
- *   targets [M] int64; rows with targets == ignore_index give zero loss and zero gradient
+ *   targets [M] int64; rows with targets == ignore_index give zero loss and zero gradient; any other
+ *           target outside [0, V) makes that row's loss NaN (the reference's criterion asserts on the
+ *           device instead)
  *   loss_rows [M], lse [M] float32 outputs (the caller reduces loss_rows; "mean" divides by the
  *   number of rows that are not ignored)
  * Backward: dlogits [M, Vp] (same dtype) = grad_scale[0] * d loss_row / d logits; the padding
@@ -175,6 +190,17 @@ int hsa_layer_norm_fwd(const void *x, const float *gamma, const float *beta, voi
 int hsa_layer_norm_bwd(const void *x, const void *dy, const float *gamma, const float *mean,
                        const float *rstd, void *dx, float *dgamma, float *dbeta, float *partial,
                        int64_t rows, int d, int dtype, void *stream);
+
+/*
+ * Strided row copy between host and device (cudaMemcpy2DAsync on `stream`): `rows` rows of `row_bytes` bytes,
+ * consecutive rows `src_pitch` / `dst_pitch` bytes apart.  kind: 0 = host to device, 1 = device to host,
+ * 2 = device to device.  No counterpart in the reference (its tensors are created on the GPU); the host-side
+ * entry point uses it to ship only the key/value rows a causal query can attend to: the leaves and the
+ * left-child parents, which are exactly the even rows N, N+2, ... of the [N leaves | parents] ordering
+ * (hierarchical_attention/ops/topology.py:49-57 masks every right sibling).
+ */
+int hsa_copy_rows_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t row_bytes,
+                        size_t rows, int kind, void *stream);
 
 /*
  * Span attention backward without any workspace argument.  No counterpart in the reference

@@ -42,6 +42,7 @@ SIGNATURES = {
     "hsa_parent_nodes_bwd": (c_int, [V] * 11 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "hsa_span_attn_fwd": (c_int, [V, V, V, V, c_void_p] + [c_int] * 8 + [c_void_p]),
     "hsa_span_attn_fwd_wait_expired": (c_int, [c_void_p]),
+    "hsa_debug_wait_test": (c_int, [ctypes.c_longlong, ctypes.c_uint]),
     "hsa_span_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 8),
     "hsa_span_attn_bwd": (c_int, [V, V, V, V, c_void_p, V, V, V, V, c_void_p, c_size_t] + [c_int] * 8 + [c_void_p]),
     "hsa_cross_entropy_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_int64,
@@ -53,6 +54,7 @@ SIGNATURES = {
     "hsa_layer_norm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float,
                                    c_int, c_void_p]),
     "hsa_layer_norm_bwd": (c_int, [c_void_p] * 9 + [c_int64, c_int, c_int, c_void_p]),
+    "hsa_copy_rows_async": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_size_t, c_size_t, c_int, c_void_p]),
     "hsa_span_attn_bwd_static": (c_int, [V, V, V, V, c_void_p, V, V, V, V] + [c_int] * 7 + [c_void_p]),
 }
 STATIC_SCRATCH_MAX_ELEMS = 1 << 20
@@ -86,6 +88,32 @@ def check(rc: int, what: str) -> None:
     if rc != 0:
         msg = load().hsa_last_error().decode(errors="replace")
         raise HsaError(f"{what} failed (code {rc}): {msg}")
+
+
+DEBUG = os.environ.get("HSA_B200_DEBUG", "0") not in ("", "0")
+_expired_seen = {}
+
+
+def wait_expired_count() -> int:
+    """CTAs on the current device whose bounded wait for their bulk copies ran out (synchronises)."""
+    count = ctypes.c_uint(0)
+    check(load().hsa_span_attn_fwd_wait_expired(ctypes.byref(count)), "hsa_span_attn_fwd_wait_expired")
+    return int(count.value)
+
+
+def debug_check_waits(what: str) -> None:
+    """With HSA_B200_DEBUG=1: synchronise after a span-attention call and raise if a CTA of it gave up waiting
+    for its copies (its tile then holds NaN).  Without the variable this does nothing: the library itself never
+    synchronises."""
+    if not DEBUG:
+        return
+    dev = torch.cuda.current_device()
+    now = wait_expired_count()
+    if now != _expired_seen.get(dev, 0):
+        before = _expired_seen.get(dev, 0)
+        _expired_seen[dev] = now
+        raise HsaError(f"{what}: {now - before} thread block(s) gave up waiting for their bulk copies; "
+                       "their output rows hold NaN")
 
 
 def dtype_code(t: torch.Tensor) -> int:

@@ -13,6 +13,8 @@ import os
 import shutil
 import subprocess
 import sys
+import tempfile
+from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
@@ -24,7 +26,7 @@ NVCC_FLAGS = [
     "-std=c++20", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-DHSA_TARGET_ARCH=100",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC",
 ]
 
 
@@ -57,16 +59,27 @@ def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: cannot build libhsa_b200.so")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-o", LIB, *sources()]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-        print(" ".join(cmd), file=sys.stderr)
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        print(res.stderr, file=sys.stderr)
+    # one nvcc per source file, in parallel, then one link step
+    with tempfile.TemporaryDirectory(prefix="hsa_b200_build_") as tmp:
+        def compile_one(src: str):
+            obj = os.path.join(tmp, os.path.basename(src)[:-3] + ".o")
+            cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-c", "-o", obj, src]
+            if verbose:
+                cmd[1:1] = ["-Xptxas", "-v"]
+            return obj, subprocess.run(cmd, capture_output=True, text=True)
+
+        with ThreadPoolExecutor(max_workers=min(len(sources()), os.cpu_count() or 1)) as pool:
+            results = list(pool.map(compile_one, sources()))
+        failed = [r for _, r in results if r.returncode != 0]
+        if failed:
+            raise RuntimeError("nvcc failed:\n" + "\n".join(r.stdout + r.stderr for r in failed))
+        if verbose:
+            for _, r in results:
+                print(r.stderr, file=sys.stderr)
+        link = subprocess.run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB,
+                               *[o for o, _ in results]], capture_output=True, text=True)
+        if link.returncode != 0:
+            raise RuntimeError("link failed:\n" + link.stdout + link.stderr)
     with open(STAMP, "w") as fh:
         fh.write(_digest())
     return LIB

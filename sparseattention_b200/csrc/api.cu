@@ -1,8 +1,10 @@
 // C ABI glue: error reporting, version, and the algorithm choice for span attention.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
 #include "hsa_common.cuh"
+#include "tma_common.cuh"
 
 namespace hsa {
 namespace {
@@ -21,9 +23,22 @@ int fail(int code, const char *fmt, ...) {
     va_end(ap);
     return code;
 }
+namespace {
+std::atomic<long long> g_wait_limit{2000000000LL};
+std::atomic<unsigned int> g_wait_extra{0u};
+}
+long long wait_limit_cycles() { return g_wait_limit.load(std::memory_order_relaxed); }
+unsigned int wait_extra_tx() { return g_wait_extra.load(std::memory_order_relaxed); }
 }  // namespace hsa
 
 using namespace hsa;
+
+extern "C" int hsa_debug_wait_test(long long limit_cycles, unsigned int extra_tx_bytes) {
+    if (limit_cycles <= 0) return fail(HSA_ERR_ARG, "hsa_debug_wait_test: the limit must be positive");
+    g_wait_limit.store(limit_cycles);
+    g_wait_extra.store(extra_tx_bytes);
+    return 0;
+}
 
 int hsa_span_attn_fwd_generic(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H,
                               int D, int radius, int causal, int dtype, cudaStream_t st);
@@ -53,7 +68,18 @@ int hsa_span_attn_bwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const
                          hsa_view dK, hsa_view dV, void *workspace, int B, int N, int H, int D, int radius, int causal,
                          int dtype, cudaStream_t st);
 
-extern "C" int hsa_version(void) { return 100; }   // 0.1.0
+extern "C" int hsa_version(void) { return 200; }   // 0.2.0
+
+extern "C" int hsa_copy_rows_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t row_bytes,
+                                   size_t rows, int kind, void *stream) {
+    HSA_CHECK_ARG(dst && src, "hsa_copy_rows_async: null pointer");
+    HSA_CHECK_ARG(kind >= 0 && kind <= 2, "hsa_copy_rows_async: kind must be 0 (host to device), 1 (device to host) or 2");
+    HSA_CHECK_ARG(row_bytes <= dst_pitch && row_bytes <= src_pitch, "hsa_copy_rows_async: a row is longer than a pitch");
+    if (rows == 0 || row_bytes == 0) return 0;
+    const cudaMemcpyKind k = kind == 0 ? cudaMemcpyHostToDevice : kind == 1 ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows, k, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : fail((int)e, "hsa_copy_rows_async: %s", cudaGetErrorString(e));
+}
 
 extern "C" const char *hsa_last_error(void) { return g_err; }
 
@@ -100,10 +126,10 @@ extern "C" int hsa_span_attn_bwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Ou
                   "hsa_span_attn_bwd: null pointer");
     HSA_CHECK_ARG(algo >= 0 && algo <= 4, "hsa_span_attn_bwd: unknown algo %d", algo);
     const size_t need = hsa_span_attn_bwd_workspace_bytes(B, N, H, D, radius, causal, dtype, algo);
-    if (workspace == nullptr || workspace_bytes < need)
+    if (need > 0 && (workspace == nullptr || workspace_bytes < need))
         return fail(HSA_ERR_WORKSPACE, "hsa_span_attn_bwd: workspace of %zu bytes needed, %zu given", need,
                     workspace_bytes);
-    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    if (need > 0 && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
         return fail(HSA_ERR_ALIGN, "hsa_span_attn_bwd: workspace must be 256-byte aligned");
     const hsa_view views[] = {Q, K, V, Out, dOut, dQ, dK, dV};
     // The 8-warp task-parallel kernel (causal, window radius <= 16) is preferred where it applies; 3 forces the

@@ -86,7 +86,9 @@ cross_entropy_fwd_kernel(const T *__restrict__ logits, int64_t row_stride, const
             lse_out[row] = lse;
             float loss = 0.f;
             if (tgt != ignore_index) {
-                const float xt = (tgt >= 0 && tgt < V) ? Traits<T>::to_f(x[tgt]) : 0.f;
+                // a target outside [0, V) that is not the ignore index is a corrupt label: the row's loss is NaN,
+                // so the mean is NaN and the caller sees it (nn.CrossEntropyLoss raises a device assertion there)
+                const float xt = (tgt >= 0 && tgt < V) ? Traits<T>::to_f(x[tgt]) : __int_as_float(0x7fffffff);
                 loss = (1.f - eps) * (lse - xt) + eps * (lse - st.sx / (float)V);
             }
             loss_rows[row] = loss;

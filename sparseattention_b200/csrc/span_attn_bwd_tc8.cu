@@ -45,22 +45,12 @@ struct SpanBwd8Args {
     // byte offsets into shared memory (the V band starts at 0)
     int kb_off, vt_off, kt_off, q_off, go_off, stat_off, tiles_off, ttiles_off, persist_off;
     float scale_log2e, scale;
+    long long wait_limit;      // cycles a CTA waits for its bulk copies
+    unsigned int extra_tx;     // 0 except in the test of the give-up path
 };
 
 // CTAs whose wait for their TMA copies ran out (never expected; added to what hsa_span_attn_fwd_wait_expired reports)
 __device__ unsigned int g_bwd8_wait_expired = 0;
-
-// Wait for phase 0 of an mbarrier, giving up after about a second.  Returns false when it gave up.
-__device__ __forceinline__ bool mbar8_wait0(uint32_t mb) {
-    uint32_t done = 0;
-    const long long start = clock64();
-    while (true) {
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done) : "r"(mb), "r"(0) : "memory");
-        if (done) return true;
-        if (clock64() - start > 2000000000LL) return false;
-    }
-}
 
 // Tree rows in shared memory: rows 8*qb .. 8*qb+7 hold what query block qb alone attends to (slots 0..7: four
 // even level-1 nodes, two even level-2 nodes, one level-3 node, the level-4 sibling of the block), row 32 the
@@ -130,6 +120,15 @@ span_bwd_tc8_kernel(const SpanBwd8Args a, const __grid_constant__ SpanBwd8Maps m
     const int nup = L - kTileLog;
     const int nps = 1 + nup;
 
+    // What a CTA does when a wait runs out: count itself and leave NaN where its results would go (its dQ rows and its
+    // partial rows of the upper levels, which the reduction kernel carries into dK / dV), so nobody mistakes them for data.
+    auto give_up = [&]() {
+        if (tid == 0) atomicAdd(&g_bwd8_wait_expired, 1u);
+        fill_rows_nan16((T *)a.dq + b * a.dq_bs + hoff + (int64_t)t0 * a.dq_rs, a.dq_rs, kTile, D, tid, 256);
+        float *mine = a.partial + (((size_t)b * a.H + h) * ntiles + tile) * nup * 2 * D;
+        for (int idx = tid; idx < nup * 2 * D; idx += 256) mine[idx] = __int_as_float(0x7fffffff);
+    };
+
     // ---------------------------------------------------------------- staging: one TMA box per thread
     // barrier 0: dOut; barrier 1: Q and the K/V bands; barrier 2: the tree rows.  Rows nobody may attend to are loaded
     // all the same (level-4 siblings of even blocks, upper levels on the causal side) or zero-filled by the copy
@@ -138,7 +137,7 @@ span_bwd_tc8_kernel(const SpanBwd8Args a, const __grid_constant__ SpanBwd8Maps m
     // group 0: dOut, 1: Q and the bands, 2: the tree rows.  TMA: bounded mbarrier wait; per-thread copies: wait_group.
     auto wait_group = [&](int g) -> bool {
         if constexpr (TMA) {
-            return mbar8_wait0(g == 0 ? mbG : g == 1 ? mbM : mbT);
+            return mbar_wait_phase0(g == 0 ? mbG : g == 1 ? mbM : mbT, a.wait_limit);
         } else {
             if (g == 0) cp_async_wait<2>(); else if (g == 1) cp_async_wait<1>(); else cp_async_wait<0>();
             return true;
@@ -155,7 +154,7 @@ span_bwd_tc8_kernel(const SpanBwd8Args a, const __grid_constant__ SpanBwd8Maps m
         const int c = tid % CPR, rg = tid / CPR;
         if constexpr (TMA) {
             if (tid == 0) {
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbG), "r"((uint32_t)BP * NH) : "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbG), "r"((uint32_t)BP * NH + a.extra_tx) : "memory");
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbM), "r"(3u * BP * NH) : "memory");
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbT), "r"(2u * (uint32_t)TP * NH) : "memory");
             }
@@ -256,9 +255,9 @@ span_bwd_tc8_kernel(const SpanBwd8Args a, const __grid_constant__ SpanBwd8Maps m
             lv[j] = (ok && c == 0) ? __ldg(a.lse + ((int64_t)b * N + n) * a.H + h) * 1.4426950408889634f : INFINITY;
         }
         if (!__syncthreads_and(wait_group(0))) {              // dOut rows are in shared memory (the wait is not expected to give up)
-            if (tid == 0) atomicAdd(&g_bwd8_wait_expired, 1u);
             wait_group(1);                                      // a second bounded chance for this CTA's copies to finish
             wait_group(2);
+            give_up();
             return;
         }
 #pragma unroll
@@ -280,8 +279,8 @@ span_bwd_tc8_kernel(const SpanBwd8Args a, const __grid_constant__ SpanBwd8Maps m
             }
         }
         if (!__syncthreads_and(wait_group(1))) {              // Q and the bands have landed; the statistics are written
-            if (tid == 0) atomicAdd(&g_bwd8_wait_expired, 1u);
             wait_group(2);
+            give_up();
             return;
         }
     }
@@ -510,7 +509,7 @@ span_bwd_tc8_kernel(const SpanBwd8Args a, const __grid_constant__ SpanBwd8Maps m
         band_pair(kb, rel, tp, tp + 512);
     }
     if (!__syncthreads_and(wait_group(2))) {         // the tree rows
-        if (tid == 0) atomicAdd(&g_bwd8_wait_expired, 1u);
+        give_up();
         return;
     }
     // ================================================================ phase 2
@@ -711,6 +710,8 @@ int hsa_span_attn_bwd_tc8(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, cons
     a.mbar_off = p.mbar_off;
     a.scale = 1.0f / sqrtf((float)D);
     a.scale_log2e = 1.4426950408889634f * a.scale;
+    a.wait_limit = wait_limit_cycles();
+    a.extra_tx = wait_extra_tx();
     SpanBwd8Maps maps{};                                       // only the 256-byte-row kernel stages by TMA
     if (D >= 128 && !bwd8_maps(Q, K, V, dOut, B, N, H, D, &maps))
         return fail(HSA_ERR_ARG, "hsa_span_attn_bwd(tc8): the driver refused a tensor map for these views");

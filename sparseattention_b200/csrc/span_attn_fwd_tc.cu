@@ -31,6 +31,8 @@ struct SpanTcArgs {
     int kv_rows;     // all rows staged per tile
     int band_box;    // rows per TMA box of the leaf band (the whole band when it fits one box)
     float scale_log2e;
+    long long wait_limit;      // cycles a CTA waits for its bulk copies
+    unsigned int extra_tx;     // 0 except in the test of the give-up path
 };
 
 // Tensor maps of one tensor (K or V), all over [B, rows, H, D] with a box of 64 elements of one head:
@@ -42,17 +44,6 @@ struct SpanTcMaps {
 
 // CTAs whose wait for their TMA copies ran out (never expected; added to what hsa_span_attn_fwd_wait_expired reports)
 __device__ unsigned int g_fwd64_wait_expired = 0;
-
-__device__ __forceinline__ bool mbar64_wait0(uint32_t mb) {       // phase 0, giving up after about a second
-    uint32_t done = 0;
-    const long long start = clock64();
-    while (true) {
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done) : "r"(mb), "r"(0) : "memory");
-        if (done) return true;
-        if (clock64() - start > 2000000000LL) return false;
-    }
-}
 
 template <typename T, int D, bool CAUSAL>
 __global__ void __launch_bounds__(128, 3)
@@ -110,7 +101,7 @@ span_fwd_tc_kernel(const SpanTcArgs a, const __grid_constant__ SpanTcMaps kmaps,
     const uint32_t mbK = smem_u32(&mbar[0]), mbV = smem_u32(&mbar[1]);
     auto wait_group = [&](int g) -> bool {                       // 0: K, 1: V
         if constexpr (TMA) {
-            return mbar64_wait0(g == 0 ? mbK : mbV);
+            return mbar_wait_phase0(g == 0 ? mbK : mbV, a.wait_limit);
         } else {
             if (g == 0) cp_async_wait<1>(); else cp_async_wait<0>();
             return true;
@@ -125,7 +116,7 @@ span_fwd_tc_kernel(const SpanTcArgs a, const __grid_constant__ SpanTcMaps kmaps,
         __syncthreads();
         if (tid == 0) {
             const uint32_t bytes = (uint32_t)PS * NH;
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbK), "r"(bytes) : "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbK), "r"(bytes + a.extra_tx) : "memory");
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV), "r"(bytes) : "memory");
         }
         // boxes of one tensor and half: band_rows / 16 band boxes, one box per level 1..5, one node per upper level
@@ -228,9 +219,15 @@ span_fwd_tc_kernel(const SpanTcArgs a, const __grid_constant__ SpanTcMaps kmaps,
         return a.band_rows + row;
     };
 
-    if (!__syncthreads_and(wait_group(0))) {             // K has landed (the wait is not expected to give up)
+    // What a CTA does when a wait runs out: count itself, leave NaN in its output rows, and go.
+    auto give_up = [&]() {
         if (tid == 0) atomicAdd(&g_fwd64_wait_expired, 1u);
+        fill_rows_nan16((T *)a.out + b * a.o_bs + hoff + (int64_t)t0 * a.o_rs, a.o_rs, kTile, D, tid, 128);
+        if (a.lse != nullptr && tid < kTile) a.lse[((int64_t)b * a.N + t0 + tid) * a.H + h] = __int_as_float(0x7fffffff);
+    };
+    if (!__syncthreads_and(wait_group(0))) {             // K has landed (the wait is not expected to give up)
         wait_group(1);                                    // a second bounded chance for this CTA's copies to finish
+        give_up();
         return;
     }
 
@@ -320,7 +317,7 @@ span_fwd_tc_kernel(const SpanTcArgs a, const __grid_constant__ SpanTcMaps kmaps,
         m0 = mn0;
         m1 = mn1;
         if (c0 == 0 && !__syncthreads_and(wait_group(1))) {        // V has landed
-            if (tid == 0) atomicAdd(&g_fwd64_wait_expired, 1u);
+            give_up();
             return;
         }
         // ---- probabilities and P.V
@@ -479,6 +476,8 @@ int hsa_span_attn_fwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float
     a.kv_rows = a.band_rows + (causal ? 31 : 62) + (a.L - kTileLog);
     a.band_box = a.band_rows <= 256 ? a.band_rows : 16;
     a.scale_log2e = 1.4426950408889634f / sqrtf((float)D);
+    a.wait_limit = wait_limit_cycles();
+    a.extra_tx = wait_extra_tx();
     SpanTcMaps km{}, vm{};                                     // only the 256-byte-row kernel stages by TMA
     if (D >= 128 && (!tc_tensor_maps(K, B, N, H, D, causal != 0, a.band_box, &km) || !tc_tensor_maps(V, B, N, H, D, causal != 0, a.band_box, &vm)))
         return fail(HSA_ERR_ARG, "hsa_span_attn_fwd(tc): the driver refused a tensor map for these views");

@@ -29,6 +29,8 @@ struct SpanTc128Args {
     int kv_rows;     // band + 63 in-tile tree rows + (L - 7) upper rows
     int plane_bytes; // one [rows][128 B] plane (rows padded to a multiple of 8)
     float scale_log2e;
+    long long wait_limit;      // cycles a CTA waits for its bulk copies
+    unsigned int extra_tx;     // 0 except in the test of the give-up path
 };
 
 constexpr int kT128 = 128, kT128Log = 7, kT128In = 63;     // causal: even nodes of levels 1..6
@@ -45,18 +47,6 @@ __device__ __forceinline__ int swz(int row, int c) { return (c & ~7) | ((c ^ row
 
 // CTAs whose wait for their bulk copies ran out (never expected; read by hsa_span_attn_fwd_wait_expired)
 __device__ unsigned int g_fwd128_wait_expired = 0;
-
-// Wait for phase 0 of an mbarrier, giving up after about a second.  Returns false when it gave up.
-__device__ __forceinline__ bool mbar_wait0(uint32_t mb) {
-    uint32_t done = 0;
-    const long long start = clock64();
-    while (true) {
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done) : "r"(mb), "r"(0) : "memory");
-        if (done) return true;
-        if (clock64() - start > 2000000000LL) return false;
-    }
-}
 
 // Tree key slot s of warp w (causal, 128-leaf tile) -> level and row inside the tile's tree storage.
 // Levels 1..3: the even nodes below the warp's 16 leaves (slots 0..6); then one node per level 4.. : the
@@ -117,7 +107,7 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
     __syncthreads();
     if (tid == 0) {
         const uint32_t bytes = (uint32_t)a.kv_rows * 128u * NH;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbK), "r"(bytes) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbK), "r"(bytes + a.extra_tx) : "memory");
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV), "r"(bytes) : "memory");
     }
     if (tid < 2 * NH * L) {
@@ -187,9 +177,15 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
         return a.band_rows + row;
     };
 
-    if (!__syncthreads_and(mbar_wait0(mbK))) {        // K has landed (the wait is not expected to give up)
+    // What a CTA does when a wait runs out: count itself, leave NaN in its output rows, and go.
+    auto give_up = [&]() {
         if (tid == 0) atomicAdd(&g_fwd128_wait_expired, 1u);
-        mbar_wait0(mbV);                              // a second bounded chance for this CTA's copies to finish
+        fill_rows_nan16((T *)a.out + b * a.o_bs + hoff + (int64_t)t0 * a.o_rs, a.o_rs, kT128, D, tid, 256);
+        if (a.lse != nullptr && tid < kT128) a.lse[((int64_t)b * N + t0 + tid) * a.H + h] = __int_as_float(0x7fffffff);
+    };
+    if (!__syncthreads_and(mbar_wait_phase0(mbK, a.wait_limit))) {        // K has landed (the wait is not expected to give up)
+        mbar_wait_phase0(mbV, a.wait_limit);                              // a second bounded chance for this CTA's copies to finish
+        give_up();
         return;
     }
 
@@ -292,8 +288,8 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
         pa[bi][3] = pack2<T>(s[bi][1][2] * i1, s[bi][1][3] * i1);
     }
 
-    if (!__syncthreads_and(mbar_wait0(mbV))) {        // V has landed
-        if (tid == 0) atomicAdd(&g_fwd128_wait_expired, 1u);
+    if (!__syncthreads_and(mbar_wait_phase0(mbV, a.wait_limit))) {        // V has landed
+        give_up();
         return;
     }
 
@@ -432,6 +428,8 @@ int hsa_span_attn_fwd_tc128(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, fl
     a.kv_rows = a.band_rows + kT128In + (a.L - kT128Log);
     a.plane_bytes = (a.kv_rows + 7) / 8 * 8 * 128;
     a.scale_log2e = 1.4426950408889634f / sqrtf((float)D);
+    a.wait_limit = wait_limit_cycles();
+    a.extra_tx = wait_extra_tx();
     SpanTc128Maps km, vm;
     if (!tensor_maps(K, B, N, H, D, a.band_rows, &km) || !tensor_maps(V, B, N, H, D, a.band_rows, &vm))
         return fail(HSA_ERR_ARG, "hsa_span_attn_fwd(tc128): the driver refused a tensor map for these views");

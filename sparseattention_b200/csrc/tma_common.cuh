@@ -50,4 +50,32 @@ inline bool map_ok(const hsa_view &v, int B, int rows, int H, int D) {
     return true;
 }
 
+// ---------------------------------------------------------------------------------- bounded mbarrier wait
+// Every kernel that waits for bulk copies gets two launch arguments from here: how long a CTA waits (clock
+// cycles, about a second unless hsa_debug_wait_test changed it) and, for the test of the give-up path only, bytes
+// added to what the first barrier of a CTA expects, so that the barrier cannot complete although every copy does.
+long long wait_limit_cycles();
+unsigned int wait_extra_tx();
+
+#ifdef __CUDACC__
+// Wait for phase 0 of an mbarrier.  Returns false when `limit` cycles ran out first.
+__device__ __forceinline__ bool mbar_wait_phase0(uint32_t mb, long long limit) {
+    uint32_t done = 0;
+    const long long start = clock64();
+    while (true) {
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done) : "r"(mb), "r"(0) : "memory");
+        if (done) return true;
+        if (clock64() - start > limit) return false;
+    }
+}
+
+// What a CTA that gave up leaves behind instead of results: NaN in every element of `rows` rows of `cols` 2-byte
+// elements (bf16 and f16 both read 0x7fff as NaN), so a consumer cannot mistake the tile for data.
+__device__ __forceinline__ void fill_rows_nan16(void *base, int64_t row_stride, int rows, int cols, int tid, int nthreads) {
+    unsigned short *p = reinterpret_cast<unsigned short *>(base);
+    for (int idx = tid; idx < rows * cols; idx += nthreads) p[(int64_t)(idx / cols) * row_stride + idx % cols] = 0x7fffu;
+}
+#endif
+
 }  // namespace hsa

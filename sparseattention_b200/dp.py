@@ -15,9 +15,12 @@ import torch.distributed as dist
 
 
 class BucketedGradAverager:
-    def __init__(self, params, bucket_bytes: int = 32 << 20, process_group=None):
+    def __init__(self, params, bucket_bytes: int = 32 << 20, process_group=None, communicate: bool = True):
+        """`communicate=False` keeps the bucket layout and the bookkeeping but leaves the collectives out
+        (each rank then trains on its own shard alone): what a benchmark compares a step against to see how
+        much of the all-reduce time is left exposed."""
         self.group = process_group
-        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.world = dist.get_world_size(process_group) if (dist.is_initialized() and communicate) else 1
         self.params = [p for p in params if p.requires_grad]
         backend = dist.get_backend(process_group) if dist.is_initialized() else "none"
         self._avg_op = backend == "nccl"            # gloo has no AVG: sum, then scale

@@ -11,6 +11,7 @@ gradient).  Differences a caller can observe:
 from __future__ import annotations
 
 import math
+import weakref
 from ctypes import c_void_p
 from typing import Dict, Optional, Tuple
 
@@ -74,7 +75,7 @@ def build_parent_nodes(Q_p, K_p, V_p, K_c, V_c):
 # The kernels derive the tree in closed form.  Tables passed by the caller are accepted for API
 # compatibility and verified (once per tensor) to be the canonical ones; anything else is refused
 # rather than silently ignored.
-_verified_tables: Dict[Tuple[int, int, int, Tuple[int, ...]], bool] = {}
+_verified_tables: Dict[int, Tuple[int, int, int]] = {}      # id(tensor) -> stamp; the entry dies with the tensor
 
 
 def _verify_tables(idx_table, mask_table, N: int) -> None:
@@ -86,8 +87,9 @@ def _verify_tables(idx_table, mask_table, N: int) -> None:
     for t, kind in ((idx_table, 0), (mask_table, 1)):
         if t is None or t.numel() == 0:
             continue
-        key = (t.data_ptr(), t._version, kind, tuple(t.shape))
-        if key in _verified_tables:
+        # a verdict is remembered per tensor OBJECT (and dropped with it), for its current version counter
+        stamp = (t._version, kind, N)
+        if _verified_tables.get(id(t)) == stamp:
             continue
         n = torch.arange(N, device=t.device).unsqueeze(1)
         l = torch.arange(L, device=t.device).unsqueeze(0)
@@ -102,9 +104,9 @@ def _verify_tables(idx_table, mask_table, N: int) -> None:
             raise _lib.HsaError(
                 "hierarchical_attention: the tables passed are not the canonical binary-tree topology "
                 "(build_tree_topology); custom topologies are not supported")
-        if len(_verified_tables) > 256:
-            _verified_tables.clear()
-        _verified_tables[key] = True
+        if id(t) not in _verified_tables:
+            weakref.finalize(t, _verified_tables.pop, id(t), None)
+        _verified_tables[id(t)] = stamp
 
 
 def span_attention_forward(Q, K, V, window_size: int, is_causal: bool, need_lse: bool = True,
@@ -124,6 +126,7 @@ def span_attention_forward(Q, K, V, window_size: int, is_causal: bool, need_lse:
                                    B, N, H, D, int(window_size), int(is_causal), _lib.dtype_code(Q), algo,
                                    _lib.stream_ptr(dev))
     _lib.check(rc, "hsa_span_attn_fwd")
+    _lib.debug_check_waits("hsa_span_attn_fwd")
     return Out, LSE
 
 
@@ -146,6 +149,7 @@ def span_attention_backward(Q, K, V, Out, LSE, dOut, window_size: int, is_causal
             *(_lib.rows_view(t) for t in (dOut, dQ, dK, dV)), c_void_p(ws.data_ptr()), ws.numel(),
             B, N, H, D, int(window_size), int(is_causal), dt, algo, _lib.stream_ptr(dev))
     _lib.check(rc, "hsa_span_attn_bwd")
+    _lib.debug_check_waits("hsa_span_attn_bwd")
     return dQ, dK, dV
 
 
@@ -182,6 +186,15 @@ def hierarchical_attention(Q, K, V, idx_table, gather_table, mask_table=None, wi
 # Host-resident inputs (inference): copy in, compute and copy out overlapped over batch chunks
 # ---------------------------------------------------------------------------------------------
 _host_streams: Dict[int, Tuple[torch.cuda.Stream, torch.cuda.Stream]] = {}
+_host_buffers: Dict[tuple, list] = {}
+
+
+def host_entry_h2d_bytes(B: int, N: int, H: int, D: int, esize: int, is_causal: bool) -> int:
+    """Bytes `hierarchical_attention_from_host` copies to the device per call: Q and, of K and V, the rows a
+    query can attend to (causal: the N leaves and the N/2 even parent rows; otherwise all 2N-1 rows)."""
+    row = H * D * esize
+    kv_rows = (N + N // 2) if (is_causal and N > 1) else (2 * N - 1)
+    return B * row * (N + 2 * kv_rows)
 
 
 def hierarchical_attention_from_host(Q, K, V, window_size=16, is_causal=True, out=None, device=None, chunks=8):
@@ -189,12 +202,17 @@ def hierarchical_attention_from_host(Q, K, V, window_size=16, is_causal=True, ou
 
     The batch is cut into `chunks` pieces; piece i+1 is copied to the device while piece i is computed and
     piece i-1 is copied back, so the call costs about max(copy-in, copy-out, compute) instead of their
-    sum.  Returns a host tensor [B,N,H,D] (`out` if given; pinned otherwise).  No autograd.
+    sum.  In the causal case only the key/value rows that can be attended to are copied: the leaves and the
+    left-child parents (the even rows from N on); the other rows of the device buffers stay zero, which is
+    what the kernels need of rows they load but mask.  Device buffers are kept per shape and reused.
+    Returns a host tensor [B,N,H,D] (`out` if given; pinned otherwise).  No autograd.
     """
+    lib = _lib.load()
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     B, N, H, D = Q.shape
     assert not Q.is_cuda and not K.is_cuda and not V.is_cuda, "inputs of this entry point live on the host"
     assert K.shape == (B, 2 * N - 1, H, D) and V.shape == K.shape
+    assert Q.is_contiguous() and K.is_contiguous() and V.is_contiguous(), "host inputs must be contiguous"
     if out is None:
         out = torch.empty((B, N, H, D), dtype=Q.dtype).pin_memory()
     if dev.index not in _host_streams:
@@ -202,26 +220,44 @@ def hierarchical_attention_from_host(Q, K, V, window_size=16, is_causal=True, ou
     work, back = _host_streams[dev.index]
     nchunk = max(1, min(int(chunks), B))
     bounds = [(B * i) // nchunk for i in range(nchunk + 1)]
+    pieces = [(lo, hi) for lo, hi in zip(bounds[:-1], bounds[1:]) if hi > lo]
+    compact = bool(is_causal) and N > 1
+    # device buffers of every piece, zero-filled once (the rows never copied must read as finite numbers)
+    key = (dev.index, B, N, H, D, Q.dtype, nchunk, compact)
+    if key not in _host_buffers:
+        if len(_host_buffers) >= 4:
+            _host_buffers.clear()
+        _host_buffers[key] = [(torch.empty((hi - lo, N, H, D), dtype=Q.dtype, device=dev),
+                               torch.zeros((hi - lo, 2 * N - 1, H, D), dtype=Q.dtype, device=dev),
+                               torch.zeros((hi - lo, 2 * N - 1, H, D), dtype=Q.dtype, device=dev)) for lo, hi in pieces]
+    buffers = _host_buffers[key]
+    row = H * D * Q.element_size()
     cur = torch.cuda.current_stream(dev)
     work.wait_stream(cur)
     back.wait_stream(cur)
     keep = []
-    for lo, hi in zip(bounds[:-1], bounds[1:]):
-        if hi == lo:
-            continue
-        with torch.cuda.stream(work):
-            q = Q[lo:hi].to(dev, non_blocking=True)
-            k = K[lo:hi].to(dev, non_blocking=True)
-            v = V[lo:hi].to(dev, non_blocking=True)
+    for (lo, hi), (q, k, v) in zip(pieces, buffers):
+        with torch.cuda.stream(work), torch.cuda.device(dev):
+            st = _lib.stream_ptr(dev)
+            q.copy_(Q[lo:hi], non_blocking=True)
+            if not compact:
+                k.copy_(K[lo:hi], non_blocking=True)
+                v.copy_(V[lo:hi], non_blocking=True)
+            else:
+                for host, devt in ((K, k), (V, v)):
+                    for j in range(hi - lo):
+                        devt[j, :N].copy_(host[lo + j, :N], non_blocking=True)               # the leaves: one block
+                        _lib.check(lib.hsa_copy_rows_async(                                  # parents N, N+2, ...
+                            c_void_p(devt[j, N].data_ptr()), 2 * row, c_void_p(host[lo + j, N].data_ptr()), 2 * row,
+                            row, N // 2, 0, st), "hsa_copy_rows_async")
             o, _ = span_attention_forward(q, k, v, window_size, is_causal, need_lse=False)
             done = torch.cuda.Event()
             done.record(work)
         with torch.cuda.stream(back):
             back.wait_event(done)
             out[lo:hi].copy_(o, non_blocking=True)
-        keep.append((q, k, v, o))
+        keep.append(o)
     cur.wait_stream(back)
-    for tensors in keep:                      # the caching allocator must not hand these out before `cur` passes
-        for t in tensors:
-            t.record_stream(cur)
+    for t in keep:                            # the caching allocator must not hand these out before `cur` passes
+        t.record_stream(cur)
     return out

@@ -5,6 +5,10 @@ loop uses it (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.p
 addition: the logits may carry padding columns beyond `num_classes` (the LM pads its vocabulary matrix
 so the LM-head GEMM stays on aligned tensor-core tiles); they are excluded from the softmax and get
 zero gradient.  The logits are read once forward and once backward, in their own dtype.
+
+Two deviations from nn.CrossEntropyLoss: a target that is neither `ignore_index` nor inside [0, num_classes)
+gives a NaN loss (PyTorch raises a device-side assertion); a batch in which every row is ignored gives 0
+(PyTorch gives NaN), because the row count is clamped to 1 without a host synchronisation.
 """
 from __future__ import annotations
 

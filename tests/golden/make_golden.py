@@ -92,12 +92,11 @@ def layer_case(tag, B, N, H, Dh, R, seed, out, subsample=1):
     gy = torch.randn(B, N - 1, dim, generator=g)
     go = torch.randn(B, N, dim, generator=g)
     sd = ref.state_dict()
-    if subsample == 1:
-        for k in WEIGHT_NAMES:
-            out[f"{tag}.{k}"] = sd[k].numpy()
-        out[f"{tag}.x"] = x.numpy()
-        out[f"{tag}.gy"] = gy.numpy()
-        out[f"{tag}.go"] = go.numpy()
+    for k in WEIGHT_NAMES:
+        out[f"{tag}.{k}"] = sd[k].numpy()
+    out[f"{tag}.x"] = x.numpy()
+    out[f"{tag}.gy"] = gy.numpy()
+    out[f"{tag}.go"] = go.numpy()
     out[f"{tag}.meta"] = np.array([B, N, H, Dh, R, seed, subsample], dtype=np.int64)
     ss = slice(None, None, subsample)
 
@@ -126,14 +125,10 @@ def layers():
     layer_case("small", 1, 64, 4, 32, 4, 200, out)
     layer_case("wide_window", 1, 32, 2, 8, 40, 300, out)      # radius larger than the sequence
     np.savez_compressed(os.path.join(HERE, "layer_eager.npz"), **out)
-    # BASELINE config 1 (B2 H4 N512 Dh64 R16 fp32): inputs and weights are re-drawn from the
-    # seed by the test (same generator calls as layer_case); only every 8th output row is kept.
+    # The fp32 layer case B2 H4 N512 Dh64 R16 (causal window 16): weights and inputs are stored in
+    # full, so the tests do not depend on re-drawing them; of the outputs every 8th row is kept.
     out = {}
     layer_case("config1", 2, 512, 4, 64, 16, 0, out, subsample=8)
-    torch.manual_seed(0)
-    ref = ref_eager.HierarchicalSparseAttentionRef(256, 4, dropout=0.0, window_size=16)
-    out["config1.weights_sha"] = np.array(hashlib.sha256(
-        b"".join(ref.state_dict()[k].numpy().tobytes() for k in WEIGHT_NAMES)).hexdigest())
     np.savez_compressed(os.path.join(HERE, "layer_config1.npz"), **out)
 
 
