@@ -118,6 +118,42 @@ int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *L
                       int H, int D, int radius, int causal, int dtype, int algo, void *stream);
 
 /*
+ * Candidate logits (weights = 0) or softmax weights (weights = 1) of span attention, one row of
+ * C = 2*radius + 1 + log2(N) float32 entries per (batch, leaf, head): out [B, N, H, C] contiguous.  Entries
+ * 0 .. 2*radius are the window slots (key leaf n - radius + c), the rest one slot per tree level; this is the
+ * layout of the `Weights` tensor HierarchicalAttentionFunc.forward saves
+ * (hierarchical_attention/ops/functional.py:131-132; kernel ops/triton/sparse_attn.py:57-145), which weights = 1
+ * reproduces: softmax over the valid slots, 0 elsewhere.  weights = 0 gives the scaled logits q.k / sqrt(D) before
+ * the softmax, -inf where a slot is outside the sequence or masked.  Portable kernel, any dtype.
+ */
+int hsa_span_attn_logits(hsa_view Q, hsa_view K, float *out, int B, int N, int H, int D, int radius,
+                         int causal, int weights, int dtype, void *stream);
+
+/*
+ * The "logits" op of the reference's first Triton prototype, build_hierarchical_logits
+ * (Hierarchical_Attention_Triton.py:456-514; kernels :327-393 and :414-454): for node rows of
+ * Q, K [B, total_nodes, H, D]
+ *   self_out  [B, seq_len, H]       float32 : scale * Q[b, t] . K[b, t]
+ *   cross_out [B, total_nodes-1, H] float32 : entry r = scale * Q[b, r^1] . K[b, r]   (each node's key scored by
+ *                                             its sibling's query; the root has no sibling)
+ * scale = 1/sqrt(D).  Either output may be NULL.  (The prototype's self-logits kernel does not compile as
+ * shipped, :389; this follows what its launcher and its commented-out body state.)
+ */
+int hsa_sibling_logits(hsa_view Q, hsa_view K, float *self_out, float *cross_out, int B, int total_nodes,
+                       int seq_len, int H, int D, int dtype, void *stream);
+
+/*
+ * Span attention of one new leaf per sequence against a key/value cache: the step of an incremental decoder.
+ * The reference's generate() re-runs the whole forward for every token
+ * (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.py:483-504); causally, leaf n needs only
+ * leaves n-radius..n and, for every set bit l of n, the left sibling of its level-l ancestor — rows that are
+ * complete once leaf n-1 has been seen.
+ *   q, out : [B, 1, H, D] (row stride unused);  K, V : [B, 2N-1, H, D] caches in the usual row order.
+ */
+int hsa_span_attn_decode(hsa_view q, hsa_view K, hsa_view V, hsa_view out, int B, int N, int H, int D,
+                         int radius, int n, int dtype, void *stream);
+
+/*
  * Diagnostic with no reference counterpart.  The TMA-staged kernels (128-leaf and 64-leaf forward, 8-warp
  * backward) wait for their bulk copies on mbarriers with a time limit (about a second).  A CTA whose wait runs
  * out counts itself, writes NaN instead of results (forward: its Out and LSE rows; backward: its dQ rows and its

@@ -206,6 +206,31 @@ def hierarchical_attention(Q, K, V, radius: int, is_causal: bool, compute_dtype=
     return out
 
 
+def span_logits(Q, K, radius: int, is_causal: bool, weights: bool = False):
+    """Candidate logits [B, N, H, 2R+1+L] of span attention (window slots, then level slots): scaled q.k, -inf at
+    masked slots; weights=True gives the softmax weights with zeros at masked slots, the `Weights` tensor of
+    hierarchical_attention/ops/functional.py:131-132 (kernel ops/triton/sparse_attn.py:57-145)."""
+    B, N, H, D = Q.shape
+    rows, valid = span_candidates(N, radius, is_causal)
+    k = K.float()[:, rows]                                       # B,N,C,H,D
+    logits = torch.einsum("bnhd,bnchd->bnhc", Q.float(), k) / math.sqrt(D)
+    logits = logits.masked_fill(~valid[None, :, None, :], float("-inf"))
+    return F.softmax(logits, dim=-1) if weights else logits
+
+
+def sibling_logits(ALL_Q, ALL_K, H: int, D: int, seq_len: int):
+    """build_hierarchical_logits of the first prototype (Hierarchical_Attention_Triton.py:456-514):
+    RES_SELF[b,t,h] = q_t.k_t / sqrt(D) for t < seq_len (:327-393, as its launcher and commented body state),
+    RES_CROSS[b,r,h] = q_{r^1}.k_r / sqrt(D) for r < total_nodes-1 (:414-454)."""
+    B, total, _ = ALL_Q.shape
+    q = ALL_Q.float().view(B, total, H, D)
+    k = ALL_K.float().view(B, total, H, D)
+    res_self = (q[:, :seq_len] * k[:, :seq_len]).sum(-1) / math.sqrt(D)
+    r = torch.arange(total - 1)
+    res_cross = (q[:, r ^ 1] * k[:, r]).sum(-1) / math.sqrt(D)
+    return res_self, res_cross
+
+
 # ---------------------------------------------------------------------------
 # Module level: the layer (restates HierarchicalSparseAttentionRef,
 # Hierarchical_Attention_Triton_Test.py:107-374; same parameter names as the package

@@ -6,7 +6,8 @@ Same public surface as the reference project's `hierarchical_attention` package
 __version__ = "0.1.0"
 
 from .modules import HierarchicalAttention
-from .ops import build_parent_nodes, build_tree_topology, generate_span_input_Y, hierarchical_attention
+from .ops import (build_hierarchical_logits, build_parent_nodes, build_tree_topology, generate_span_input_Y,
+                  hierarchical_attention)
 
 __all__ = [
     "HierarchicalAttention",
@@ -14,5 +15,6 @@ __all__ = [
     "generate_span_input_Y",
     "build_parent_nodes",
     "hierarchical_attention",
+    "build_hierarchical_logits",       # the logits op of the reference's first prototype (Hierarchical_Attention_Triton.py:456)
     "__version__",
 ]

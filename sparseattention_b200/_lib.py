@@ -54,6 +54,9 @@ SIGNATURES = {
     "hsa_layer_norm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float,
                                    c_int, c_void_p]),
     "hsa_layer_norm_bwd": (c_int, [c_void_p] * 9 + [c_int64, c_int, c_int, c_void_p]),
+    "hsa_span_attn_logits": (c_int, [V, V, c_void_p] + [c_int] * 8 + [c_void_p]),
+    "hsa_sibling_logits": (c_int, [V, V, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p]),
+    "hsa_span_attn_decode": (c_int, [V, V, V, V] + [c_int] * 7 + [c_void_p]),
     "hsa_copy_rows_async": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_size_t, c_size_t, c_int, c_void_p]),
     "hsa_span_attn_bwd_static": (c_int, [V, V, V, V, c_void_p, V, V, V, V] + [c_int] * 7 + [c_void_p]),
 }

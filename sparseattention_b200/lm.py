@@ -132,6 +132,126 @@ class TransformerLM(nn.Module):
         return logits if padded_logits else logits[..., : self.vocab_size]
 
 
+class IncrementalDecoder:
+    """Token-by-token evaluation of a TransformerLM with per-layer caches, giving the logits the full forward
+    would give at each position without re-running it (the reference's generate() re-runs the whole model for
+    every new token: Hierarchical_Transformer_Pretrain.py:483-504).
+
+    It rests on the layer being causal: leaf n attends to leaves <= n and to LEFT sibling nodes only, and a
+    node's value depends only on the leaves under it.  So everything computed for position n stays valid, and
+    a parent node is computed exactly once, when its last leaf arrives (node j of level l completes at
+    n = (j+1) * 2^l - 1).  Per layer the decoder keeps, for every leaf and completed node: the child key/value
+    projections the bottom-up pass consumes (Wk_y / Wv_y of the row's output), the parent stream y entering
+    the layer, and the key/value rows of the top-down pass (Wk_x / Wv_x).  One step costs O(log N) rows per layer.
+
+    `capacity` (a power of two) is the longest sequence the caches hold; logits at position n equal those of
+    model(tokens[:, :M])[:, n] for any power-of-two M > n, in eval mode.
+    """
+
+    def __init__(self, model: "TransformerLM", batch: int, capacity: int, dtype: Optional[torch.dtype] = None):
+        assert capacity >= 2 and capacity & (capacity - 1) == 0, "capacity must be a power of two"
+        self.model = model.eval()
+        p = next(model.parameters())
+        self.dev, self.dtype = p.device, (dtype or p.dtype)
+        self.B, self.N, self.d = batch, capacity, model.d_model
+        rows = 2 * capacity - 1
+        attn0 = model.layers[0].self_attn
+        self.H, self.Dh = attn0.num_heads, attn0.head_dim
+        new = lambda *shape: torch.zeros(*shape, dtype=self.dtype, device=self.dev)   # noqa: E731
+        nl = len(model.layers)
+        self.y0 = new(batch, rows, self.d)                       # row r: x0 of leaf r, or the initial value of node r
+        self.y_in = [new(batch, rows, self.d) for _ in range(nl + 1)]      # parent stream entering layer i (node rows)
+        self.kc = [new(batch, rows, self.H, self.Dh) for _ in range(nl)]   # Wk_y of each row's bottom-up output
+        self.vc = [new(batch, rows, self.H, self.Dh) for _ in range(nl)]
+        self.K = [new(batch, rows, self.H, self.Dh) for _ in range(nl)]    # top-down keys / values
+        self.V = [new(batch, rows, self.H, self.Dh) for _ in range(nl)]
+        self.n = 0
+
+    @staticmethod
+    def _row(N: int, level: int, j: int) -> int:
+        return j if level == 0 else 2 * N - (N >> (level - 1)) + j
+
+    @torch.no_grad()
+    def step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Consume the tokens [B] of position self.n; returns the logits [B, vocab_size] of that position."""
+        from .ops.functional import build_parent_nodes, span_attention_decode
+        m, n, N, B, H, Dh = self.model, self.n, self.N, self.B, self.H, self.Dh
+        assert n < N, "cache capacity exhausted"
+        x = m.embedding(tokens.view(B)) * math.sqrt(self.d) + m.pos_encoding.pe[0, n]
+        x = x.to(self.dtype)
+        # levels whose node completes with this leaf: 1 .. (number of trailing ones of n)
+        done = 0
+        while done < N.bit_length() - 1 and (n >> done) & 1:
+            done += 1
+        # initial parents (pairwise means of the level below; generate_span_input_Y)
+        self.y0[:, n] = x
+        for l in range(1, done + 1):
+            j = n >> l
+            c0 = self._row(N, l - 1, 2 * j)
+            self.y0[:, self._row(N, l, j)] = 0.5 * self.y0[:, c0] + 0.5 * self.y0[:, c0 + 1]
+            self.y_in[0][:, self._row(N, l, j)] = self.y0[:, self._row(N, l, j)]
+        for i, layer in enumerate(m.layers):
+            at = layer.self_attn
+            lin = lambda w, t: F.linear(t, w.weight)               # noqa: E731
+            heads = lambda t: t.view(B, 1, H, Dh)                  # noqa: E731
+            # ---- bottom-up: this leaf's child projections, then every node that completes now
+            self.kc[i][:, n] = lin(at.Wk_y, x).view(B, H, Dh)
+            self.vc[i][:, n] = lin(at.Wv_y, x).view(B, H, Dh)
+            for l in range(1, done + 1):
+                j = n >> l
+                r = self._row(N, l, j)
+                c0 = self._row(N, l - 1, 2 * j)
+                y_prev = self.y_in[i][:, r]
+                y_norm = layer.norm_y(y_prev)
+                out = build_parent_nodes(heads(lin(at.Wq_y, y_norm)), heads(lin(at.Wk_y, y_norm)), heads(lin(at.Wv_y, y_norm)),
+                                         self.kc[i][:, c0:c0 + 2], self.vc[i][:, c0:c0 + 2]).reshape(B, self.d)
+                self.kc[i][:, r] = lin(at.Wk_y, out).view(B, H, Dh)
+                self.vc[i][:, r] = lin(at.Wv_y, out).view(B, H, Dh)
+                y_next = y_prev + at.out_proj_y(out)
+                self.y_in[i + 1][:, r] = y_next
+                self.K[i][:, r] = lin(at.Wk_x, y_next).view(B, H, Dh)
+                self.V[i][:, r] = lin(at.Wv_x, y_next).view(B, H, Dh)
+            # ---- top-down: the new leaf against the caches
+            xn = layer.norm1(x)
+            self.K[i][:, n] = lin(at.Wk_x, xn).view(B, H, Dh)
+            self.V[i][:, n] = lin(at.Wv_x, xn).view(B, H, Dh)
+            ctx = span_attention_decode(lin(at.Wq_x, xn).view(B, H, Dh), self.K[i], self.V[i], n, at.window_size)
+            x = x + at.out_proj_x(ctx.reshape(B, self.d))
+            x = x + layer.feed_forward(layer.norm2(x))
+        self.n += 1
+        return m.fc_out(x)[:, : m.vocab_size]
+
+
+@torch.no_grad()
+def generate(model: "TransformerLM", prompt: torch.Tensor, max_len: int = 50, temperature: float = 1.0,
+             eos_token: Optional[int] = 3, generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    """Sampling loop of the reference's TransformerLM.generate (Hierarchical_Transformer_Pretrain.py:483-504:
+    softmax(logits / temperature), multinomial, stop at the EOS id when the batch is a single sequence), run
+    incrementally: the prompt is fed token by token, then one decoder step per generated token."""
+    if prompt.dim() == 1:
+        prompt = prompt.unsqueeze(0)
+    dev = next(model.parameters()).device
+    prompt = prompt.to(dev)
+    B, P = prompt.shape
+    assert P + max_len <= model.pos_encoding.pe.size(1), "prompt + max_len exceeds the positional table"
+    capacity = 1 << max(1, (P + max_len - 1).bit_length())
+    dec = IncrementalDecoder(model, B, capacity)
+    logits = None
+    for t in range(P):
+        logits = dec.step(prompt[:, t])
+    tokens = prompt
+    for _ in range(max_len):
+        probs = F.softmax(logits.float() / temperature, dim=-1)
+        nxt = torch.multinomial(probs, 1, generator=generator)
+        tokens = torch.cat([tokens, nxt], dim=1)
+        if eos_token is not None and B == 1 and int(nxt) == eos_token:
+            break
+        if dec.n >= dec.N:
+            break
+        logits = dec.step(nxt.view(B))
+    return tokens
+
+
 def zipf_tokens(batch: int, length: int, vocab: int, seed: int, s: float = 1.1, device="cpu") -> torch.Tensor:
     """[batch, length] token ids, rank r drawn with probability proportional to r^-s (id = r - 1)."""
     gen = torch.Generator().manual_seed(seed)

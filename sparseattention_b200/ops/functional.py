@@ -153,6 +153,65 @@ def span_attention_backward(Q, K, V, Out, LSE, dOut, window_size: int, is_causal
     return dQ, dK, dV
 
 
+def span_attention_logits(Q, K, window_size: int, is_causal: bool, weights: bool = False):
+    """Per-leaf candidate logits of span attention, float32 [B, N, H, 2*window_size + 1 + log2 N]: window slots
+    (key leaf n - window_size + c) first, then one slot per tree level.  weights=False: q.k / sqrt(D), -inf where
+    a slot is masked or outside the sequence; weights=True: the softmax weights (0 where masked), i.e. the
+    `Weights` tensor the reference's forward saves (ops/functional.py:131-132).  No autograd."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(Q, K)
+    Q, K = _lib.as_rows(Q), _lib.as_rows(K)
+    B, N, H, D = Q.shape
+    assert K.shape == (B, 2 * N - 1, H, D) and K.dtype == Q.dtype, "K must be [B, 2N-1, H, D] of Q's dtype"
+    L = int(math.log2(N)) if N > 1 else 0
+    out = torch.empty((B, N, H, 2 * int(window_size) + 1 + L), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.hsa_span_attn_logits(_lib.rows_view(Q), _lib.rows_view(K), c_void_p(out.data_ptr()), B, N, H, D,
+                                      int(window_size), int(is_causal), int(weights), _lib.dtype_code(Q),
+                                      _lib.stream_ptr(dev))
+    _lib.check(rc, "hsa_span_attn_logits")
+    return out
+
+
+def build_hierarchical_logits(ALL_Q, ALL_K, H: int, D: int, seq_len: int):
+    """The logits op of the reference's first prototype (Hierarchical_Attention_Triton.py:456), same signature:
+    ALL_Q, ALL_K [B, total_nodes, H*D] -> (RES_SELF [B, seq_len, H], RES_CROSS [B, total_nodes-1, H]), float32;
+    RES_SELF[b,t] = q_t.k_t / sqrt(D), RES_CROSS[b,r] = q_{r^1}.k_r / sqrt(D) (a node's key against its sibling's
+    query).  No autograd (the prototype is forward only)."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(ALL_Q, ALL_K)
+    B, total, DH = ALL_Q.shape
+    assert DH == H * D and ALL_K.shape == ALL_Q.shape and ALL_K.dtype == ALL_Q.dtype
+    q = ALL_Q.contiguous().view(B, total, H, D)
+    k = ALL_K.contiguous().view(B, total, H, D)
+    res_self = torch.empty((B, seq_len, H), dtype=torch.float32, device=dev)
+    res_cross = torch.empty((B, total - 1, H), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.hsa_sibling_logits(_lib.rows_view(q), _lib.rows_view(k), c_void_p(res_self.data_ptr()),
+                                    c_void_p(res_cross.data_ptr()), B, total, int(seq_len), H, D, _lib.dtype_code(q),
+                                    _lib.stream_ptr(dev))
+    _lib.check(rc, "hsa_sibling_logits")
+    return res_self, res_cross
+
+
+def span_attention_decode(q, K, V, n: int, window_size: int):
+    """Span attention of the single new leaf `n` of every sequence: q [B, H, D] (or [B, 1, H, D]) against the
+    key/value caches K, V [B, 2N-1, H, D]; only rows of leaves <= n and of completed left siblings are read.
+    Returns [B, H, D].  No autograd."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(q, K, V)
+    B, rows, H, D = K.shape
+    N = (rows + 1) // 2
+    q4 = q.reshape(B, 1, H, D).contiguous()
+    K, V = _lib.as_rows(K), _lib.as_rows(V)
+    out = torch.empty_like(q4)
+    with torch.cuda.device(dev):
+        rc = lib.hsa_span_attn_decode(_lib.rows_view(q4), _lib.rows_view(K), _lib.rows_view(V), _lib.rows_view(out),
+                                      B, N, H, D, int(window_size), int(n), _lib.dtype_code(q4), _lib.stream_ptr(dev))
+    _lib.check(rc, "hsa_span_attn_decode")
+    return out.view(B, H, D)
+
+
 class HierarchicalAttentionFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K, V, idx_table, gather_table, mask_table=None, window_size=16):

@@ -172,12 +172,53 @@ def triton_ops():
     np.savez_compressed(os.path.join(HERE, "triton_ops.npz"), **out)
 
 
+def logits_ops():
+    """(1) The softmax weights the package's forward saves (its `Weights` tensor, ops/functional.py:131-132),
+    taken from the unmodified forward run by the Triton interpreter.  (2) The cross logits of the first prototype's
+    build_hierarchical_logits (Hierarchical_Attention_Triton.py:414-454), its kernel launched as the prototype's
+    own launcher does (:487-497); the prototype's self-logits kernel cannot be launched as shipped."""
+    from hierarchical_attention.ops.functional import HierarchicalAttentionFunc
+
+    class Ctx:
+        def save_for_backward(self, *tensors):
+            self.saved = tensors
+
+    out = {}
+    g = torch.Generator().manual_seed(17)
+    for tag, (B, N, H, D, R) in {"w_a": (2, 16, 3, 16, 2), "w_b": (1, 32, 2, 8, 5), "w_r0": (1, 8, 2, 16, 0)}.items():
+        Q = torch.randn(B, N, H, D, generator=g)
+        K = torch.randn(B, 2 * N - 1, H, D, generator=g)
+        V = torch.randn(B, 2 * N - 1, H, D, generator=g)
+        out[f"{tag}.meta"] = np.array([B, N, H, D, R], dtype=np.int64)
+        out[f"{tag}.Q"], out[f"{tag}.K"] = Q.numpy(), K.numpy()
+        for causal in (True, False):
+            t = build_tree_topology(N, is_causal=causal, device="cpu")
+            ctx = Ctx()
+            HierarchicalAttentionFunc.forward(ctx, Q, K, V, t["forward_idx"], t["backward_gather"],
+                                              t["forward_mask"] if causal else None, R)
+            out[f"{tag}.weights_c{int(causal)}"] = ctx.saved[5].numpy()
+    spec = importlib.util.spec_from_file_location("ref_v1", os.path.join(REF, "Hierarchical_Attention_Triton.py"))
+    v1 = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(v1)
+    B, N, H, D = 2, 16, 4, 16                       # the prototype's kernels need a power-of-two head count
+    total = 2 * N - 1
+    Q = torch.randn(B, total, H * D, generator=g)
+    K = torch.randn(B, total, H * D, generator=g)
+    res = torch.empty(B, total - 1, H)
+    v1.hierarchical_cross_logits_kernel_opt[(total - 1, B)](Q, K, res, *Q.stride(), *res.stride(), H=H, D=D,
+                                                            BLOCK_SIZE_D=32, num_warps=4)
+    out["v1.meta"] = np.array([B, N, H, D], dtype=np.int64)
+    out["v1.ALL_Q"], out["v1.ALL_K"], out["v1.RES_CROSS"] = Q.numpy(), K.numpy(), res.numpy()
+    np.savez_compressed(os.path.join(HERE, "logits_ops.npz"), **out)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     topology()
     span_y()
     layers()
     triton_ops()
+    logits_ops()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

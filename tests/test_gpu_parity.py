@@ -342,6 +342,64 @@ def test_span_attention_full_size_properties(hsa):
     assert rel_err(lse[:, sample].cpu(), torch.logsumexp(logits, dim=-1)) < 1e-4
 
 
+# ------------------------------------------------------------------------------------- logits ops
+def test_logits_ops_golden(hsa, golden):
+    """Span-attention weights against the tensor the reference's forward saves; the first prototype's cross logits
+    against its own kernel (both run by the Triton interpreter when the fixture was made)."""
+    from sparseattention_b200.ops import functional as F
+    g = golden("logits_ops.npz")
+    for tag in ("w_a", "w_b", "w_r0"):
+        B, N, H, D, R = (int(v) for v in g[f"{tag}.meta"])
+        for c in (1, 0):
+            w = F.span_attention_logits(dev(g[f"{tag}.Q"]), dev(g[f"{tag}.K"]), R, bool(c), weights=True)
+            assert w.shape == (B, N, H, 2 * R + 1 + int(math.log2(N)))
+            assert rel_err(w.cpu(), g[f"{tag}.weights_c{c}"]) < 1e-5, (tag, c)
+    B, N, H, D = (int(v) for v in g["v1.meta"])
+    rs, rc = hsa.build_hierarchical_logits(dev(g["v1.ALL_Q"]), dev(g["v1.ALL_K"]), H, D, N)
+    assert rel_err(rc.cpu(), g["v1.RES_CROSS"]) < 1e-5
+    want_self, _ = orc.sibling_logits(torch.from_numpy(g["v1.ALL_Q"]), torch.from_numpy(g["v1.ALL_K"]), H, D, N)
+    assert rel_err(rs.cpu(), want_self) < 1e-5
+
+
+@pytest.mark.parametrize("case", [(1, 1, 1, 8, 2), (2, 16, 3, 24, 2), (1, 64, 2, 32, 5), (1, 64, 4, 64, 100),
+                                  (2, 256, 3, 64, 8), (1, 512, 12, 64, 16), (1, 32, 1, 200, 3)])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_span_logits_vs_oracle(hsa, case, causal, dtype):
+    from sparseattention_b200.ops import functional as F
+    B, N, H, D, R = case
+    gen = torch.Generator().manual_seed(N + R)
+    Q = torch.randn(B, N, H, D, generator=gen).to(dtype)
+    K = torch.randn(B, 2 * N - 1, H, D, generator=gen).to(dtype)
+    want = orc.span_logits(Q, K, R, causal)
+    got = F.span_attention_logits(Q.cuda(), K.cuda(), R, causal).cpu()
+    inf = want == float("-inf")
+    assert torch.equal(got == float("-inf"), inf)                                  # the same slots are masked
+    assert rel_err(got.masked_fill(inf, 0), want.masked_fill(inf, 0)) < 1e-5      # float32 accumulation either way
+    w = F.span_attention_logits(Q.cuda(), K.cuda(), R, causal, weights=True).cpu()
+    assert rel_err(w, orc.span_logits(Q, K, R, causal, weights=True)) < 1e-5
+    # the weights are those of the attention output: sum_c w_c v_c equals the forward
+    V = torch.randn(B, 2 * N - 1, H, D, generator=gen).to(dtype)
+    rows, _ = orc.span_candidates(N, R, causal)
+    out = torch.einsum("bnhc,bnchd->bnhd", w, V.float()[:, rows])
+    fwd, _ = F.span_attention_forward(Q.cuda(), K.cuda(), V.cuda(), R, causal, algo=1)
+    assert rel_err(fwd.float().cpu(), out) < TOL[dtype]
+
+
+@pytest.mark.parametrize("shape", [(1, 3, 1, 8), (2, 31, 3, 16), (1, 127, 8, 64), (2, 15, 12, 64)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sibling_logits_vs_oracle(hsa, shape, dtype):
+    B, total, H, D = shape
+    N = (total + 1) // 2
+    gen = torch.Generator().manual_seed(total)
+    Q = torch.randn(B, total, H * D, generator=gen).to(dtype)
+    K = torch.randn(B, total, H * D, generator=gen).to(dtype)
+    want_self, want_cross = orc.sibling_logits(Q, K, H, D, N)
+    rs, rc = hsa.build_hierarchical_logits(Q.cuda(), K.cuda(), H, D, N)
+    assert rs.dtype == torch.float32 and rs.shape == (B, N, H) and rc.shape == (B, total - 1, H)
+    assert rel_err(rs.cpu(), want_self) < 1e-5 and rel_err(rc.cpu(), want_cross) < 1e-5
+
+
 # ------------------------------------------------------------------------------------- the layer
 def _module_pair(hsa, g, tag):
     B, N, H, Dh, R, seed, sub = (int(v) for v in g[f"{tag}.meta"])
@@ -529,6 +587,59 @@ def test_language_model_bf16_autocast_training_step(hsa):
     for name in ("embedding.weight", "layers.0.self_attn.Wk_y.weight", "layers.1.self_attn.Wq_x.weight",
                  "layers.0.norm_y.weight", "layers.1.feed_forward.fc2.weight"):
         assert rel_err(got[name].grad.float().cpu(), want[name].grad) < 2e-2, name
+
+
+# ------------------------------------------------------------------------------------- incremental decoding
+@pytest.mark.parametrize("case", [(2, 16, 3, 24, 2), (1, 64, 2, 32, 5), (3, 256, 4, 64, 16), (1, 1024, 12, 64, 16)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_span_attention_decode_vs_oracle(hsa, case, dtype):
+    """The single-leaf op against the oracle's causal span attention evaluated at that leaf; rows of later leaves
+    and of nodes that are not complete yet hold NaN in the cache, so reading any of them would show."""
+    from sparseattention_b200.ops import functional as F
+    B, N, H, D, R = case
+    gen = torch.Generator().manual_seed(N * 3 + R)
+    Q = torch.randn(B, N, H, D, generator=gen).to(dtype)
+    K = torch.randn(B, 2 * N - 1, H, D, generator=gen).to(dtype)
+    V = torch.randn(B, 2 * N - 1, H, D, generator=gen).to(dtype)
+    for n in sorted({0, 1, 2, 5, N // 2 - 1, N // 2, N - 2, N - 1}):
+        if n < 0 or n >= N:
+            continue
+        want = orc.hierarchical_attention(Q, K, V, R, True, leaves=torch.tensor([n]))[:, 0]
+        Kc, Vc = K.clone(), V.clone()
+        Kc[:, n + 1:N] = float("nan")
+        Vc[:, n + 1:N] = float("nan")
+        for lvl in range(1, int(math.log2(N)) + 1):     # a node is complete when the last leaf under it is <= n
+            base = 2 * N - (N >> (lvl - 1))
+            for j in range(N >> lvl):
+                if (j + 1) * (1 << lvl) - 1 > n:
+                    Kc[:, base + j] = float("nan")
+                    Vc[:, base + j] = float("nan")
+        got = F.span_attention_decode(Q[:, n].cuda(), Kc.cuda(), Vc.cuda(), n, R)
+        assert rel_err(got.float().cpu(), want) < TOL[dtype], n
+
+
+def test_incremental_decoder_matches_full_forward(hsa):
+    """IncrementalDecoder logits at every position equal the full forward's (fp32), for a cache exactly as long as the
+    sequence and for a longer one; generate() returns prompt + sampled tokens."""
+    from sparseattention_b200.lm import IncrementalDecoder, TransformerLM, generate, zipf_tokens
+    torch.backends.cuda.matmul.allow_tf32 = False
+    vocab, d, heads, ff, layers, N = 211, 64, 4, 128, 2, 32
+    torch.manual_seed(7)
+    model = TransformerLM(vocab, d, heads, ff, layers, dropout=0.1, window_size=4).cuda().eval()
+    tokens = zipf_tokens(2, N, vocab, seed=3).cuda()
+    with torch.no_grad():
+        full = model(tokens)
+    for capacity in (N, 2 * N):
+        dec = IncrementalDecoder(model, 2, capacity)
+        for n in range(N):
+            logits = dec.step(tokens[:, n])
+            assert rel_err(logits.cpu(), full[:, n].cpu()) < 1e-4, (capacity, n)
+    # a prefix of a longer sequence sees the same logits (causality of the whole model)
+    with torch.no_grad():
+        half = model(tokens[:, : N // 2])
+    assert rel_err(half.cpu(), full[:, : N // 2].cpu()) < 1e-4
+    out = generate(model, tokens[0, :5], max_len=6, eos_token=None, generator=torch.Generator(device="cuda").manual_seed(1))
+    assert out.shape == (1, 11) and torch.equal(out[0, :5], tokens[0, :5]) and int(out.max()) < vocab
 
 
 # ------------------------------------------------------------------------------------- dropout

@@ -137,3 +137,17 @@ def test_ops_against_triton_interpreter(golden):
             assert rel_err(q.grad, g[f"{tag}.dQ_c{c}"]) < 1e-5
             assert rel_err(k.grad, g[f"{tag}.dK_c{c}"]) < 1e-5
             assert rel_err(v.grad, g[f"{tag}.dV_c{c}"]) < 1e-5
+
+
+def test_logits_ops_against_reference(golden):
+    g = golden("logits_ops.npz")
+    for tag in ("w_a", "w_b", "w_r0"):
+        B, N, H, D, R = (int(v) for v in g[f"{tag}.meta"])
+        for c in (1, 0):
+            w = orc.span_logits(torch.from_numpy(g[f"{tag}.Q"]), torch.from_numpy(g[f"{tag}.K"]), R, bool(c), weights=True)
+            assert rel_err(w, g[f"{tag}.weights_c{c}"]) < 1e-5
+            lg = orc.span_logits(torch.from_numpy(g[f"{tag}.Q"]), torch.from_numpy(g[f"{tag}.K"]), R, bool(c))
+            assert bool(((lg == float("-inf")) == (torch.from_numpy(g[f"{tag}.weights_c{c}"]) == 0)).all())
+    B, N, H, D = (int(v) for v in g["v1.meta"])
+    _, cross = orc.sibling_logits(torch.from_numpy(g["v1.ALL_Q"]), torch.from_numpy(g["v1.ALL_K"]), H, D, N)
+    assert rel_err(cross, g["v1.RES_CROSS"]) < 1e-5
