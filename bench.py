@@ -402,10 +402,44 @@ def kernel_loops(workload, device):
     }, state
 
 
+def gemm_table(device, steps=20):
+    """The dense products of one LM training step (8 x 4096 tokens, d_model 512, FFN 2048, padded vocabulary 50304) on
+    the library's tcgen05 kernel and, beside it, on torch.matmul (the vendor library): TFLOP/s each."""
+    from sparseattention_b200.ops.gemm import gemm
+    rows = 8 * 4096
+    shapes = [("qkv_y  Y=XW^T", rows, 1536, 512), ("kv     Y=XW^T", rows, 1024, 512), ("proj   Y=XW^T", rows, 512, 512),
+              ("fc1    Y=XW^T", rows, 2048, 512), ("fc2    Y=XW^T", rows, 512, 2048), ("head   Y=XW^T", rows, 50304, 512)]
+    _, tf_peak, _ = measured_peaks()
+    out = []
+    gen = torch.Generator(device=device).manual_seed(3)
+    for name, M, N, K in shapes:
+        X = torch.randn(M, K, generator=gen, device=device, dtype=torch.bfloat16)
+        W = torch.randn(N, K, generator=gen, device=device, dtype=torch.bfloat16)
+        dY = torch.randn(M, N, generator=gen, device=device, dtype=torch.bfloat16)
+        flops = 2.0 * M * N * K
+        rec = {"product": name.split()[0], "M": M, "N": N, "K": K}
+        for kind, ours, lib in (
+                ("fwd", lambda: gemm(X, W), lambda: torch.matmul(X, W.t())),
+                ("dx", lambda: gemm(dY, W, b_t=True), lambda: torch.matmul(dY, W)),
+                ("dw", lambda: gemm(dY.unsqueeze(0), X.unsqueeze(0), a_t=True, b_t=True, out_dtype=torch.float32),
+                 lambda: torch.matmul(dY.t(), X))):
+            mo = time_cuda(ours, steps, 3, lambda: None) / steps
+            ml = time_cuda(lib, steps, 3, lambda: None) / steps
+            rec[kind] = {"ours_ms": mo, "ours_tflops": flops / (mo * 1e-3) / 1e12, "library_ms": ml,
+                         "library_tflops": flops / (ml * 1e-3) / 1e12,
+                         "frac_of_sustained_peak": flops / (mo * 1e-3) / 1e12 / tf_peak}
+        out.append(rec)
+        del X, W, dY
+    return out
+
+
 def run_only(args):
     """One kernel loop on the chosen workload (what profiler captures are taken from)."""
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
+    if args.only == "gemm":
+        emit({"only": "gemm", "products": gemm_table(device, max(3, min(args.steps, 20)))})
+        return
     if args.only == "reference_triton":
         emit(reference_triton_child(args, device))
         return
@@ -739,7 +773,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="layer_n4096", choices=sorted(WORKLOADS))
-    ap.add_argument("--only", default=None, choices=["fwd", "bwd", "parents", "parents_bwd", "lm", "reference_triton"],
+    ap.add_argument("--only", default=None, choices=["fwd", "bwd", "parents", "parents_bwd", "lm", "reference_triton", "gemm"],
                     help="run one kernel loop (or the LM step, or the reference's Triton package) and print a short JSON line")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--sustained-seconds", type=float, default=2.5)

@@ -228,6 +228,63 @@ int hsa_layer_norm_bwd(const void *x, const void *dy, const float *gamma, const 
                        int64_t rows, int d, int dtype, void *stream);
 
 /*
+ * Dense product on the tcgen05 tensor cores, for the contractions of the layer that share a dense operand: the
+ * projections Wq/Wk/Wv/out_proj (hierarchical_attention/modules/attention.py:101-103,116-117,141-142,162,182-187,220
+ * call nn.Linear for each), the feed-forward pair and the LM head of the model around it
+ * (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.py:331-340,480), and their backward products.
+ *
+ *   C[b, m, n] (+)= sum_k A[b, m, k] * B[n, k] (+ bias[n])        bfloat16 operands, float32 accumulation
+ *
+ *   a_layout 0: A is stored [batches, rows, K] (hsa_view strides);  B is one matrix for all batch entries:
+ *               b_layout 0: stored [N, K] (an nn.Linear weight: Y = X W^T);  b_layout 1: stored [K, N] (dX = dY W).
+ *               C : [batches, rows, N].
+ *   a_layout 1: A is stored [batches, K, rows] and B [batches, K, N] (b_layout must be 1): the sum runs over k AND
+ *               over the batch entries, C : [rows, N] (one matrix: dW = dY^T X over all tokens).
+ *   out_dtype HSA_BF16 or HSA_F32; accumulate != 0 adds to C (float32 only); bias: float32 [N] or NULL.
+ *   splits > 1 cuts the K range into that many pieces (for few-tile, long-K products); their float32 partial tiles go
+ *   to `workspace` (hsa_gemm_workspace_bytes, 256-byte aligned) and are summed in split order: deterministic.
+ *   hsa_gemm_choose_splits suggests a count that fills the GPU.
+ * N a multiple of 8 (and rows, with a_layout 1); pointers and strides 16-byte aligned.  hsa_gemm_aborts: number of thread blocks (since the
+ * library was loaded, current device) that gave up a bounded wait on an mbarrier; 0 in a healthy run; synchronises.
+ */
+/*
+ * Element-wise tail fused into the product's epilogue (hsa_gemm_ex, splits == 1, a_layout == 0), applied in this
+ * order to v = acc + bias:  relu;  dropout on columns [drop_col_begin, drop_col_end) (kept entries times drop_scale);
+ * gate (v = gate > 0 ? v * gate_scale : 0, gate a bfloat16 tensor shaped like the output: the backward of
+ * relu + dropout given their forward output);  + residual (float32, shaped like the output);  then the store, and
+ * for float32 outputs optionally a bfloat16 copy of the stored values.  These are the element-wise steps the
+ * reference runs as separate kernels around its nn.Linear calls: dropout of the value projections
+ * (hierarchical_attention/modules/attention.py:117,135,142,187), bias + dropout + residual of the decoder layer
+ * (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.py:406,419,424), relu + dropout of the
+ * feed-forward (:337-340).
+ * Dropout masks are a pure function of (*rng_state, site, element id), element id = position in the logical
+ * [batches, drop_rows_total, N] tensor (this product writes rows drop_row_offset .. of it); hsa_dropout_apply
+ * regenerates them.  drop_site1 != 0 applies a second, independent mask (values dropped twice).
+ * drop_threshold = p * 2^32, drop_scale = 1/(1-p) (squared with two masks).  A zeroed struct is "no tail".
+ */
+typedef struct hsa_gemm_epilogue {
+    int relu;
+    const unsigned long long *rng_state;      /* device; NULL = no dropout */
+    unsigned int drop_site0, drop_site1, drop_threshold;
+    float drop_scale;
+    int drop_col_begin, drop_col_end;
+    long long drop_rows_total, drop_row_offset;
+    const void *gate; long long gate_bs, gate_rs; float gate_scale;
+    const float *residual; long long res_bs, res_rs;
+    void *copy_bf16; long long copy_bs, copy_rs;
+} hsa_gemm_epilogue;
+
+size_t hsa_gemm_workspace_bytes(int batches, int rows, int N, int K, int a_layout, int b_layout, int splits);
+int hsa_gemm_choose_splits(int batches, int rows, int N, int K);
+int hsa_gemm(hsa_view A, hsa_view B, hsa_view C, const float *bias, int batches, int rows, int N, int K,
+             int a_layout, int b_layout, int out_dtype, int accumulate, int splits, void *workspace,
+             size_t workspace_bytes, void *stream);
+int hsa_gemm_ex(hsa_view A, hsa_view B, hsa_view C, const float *bias, int batches, int rows, int N, int K,
+                int a_layout, int b_layout, int out_dtype, int accumulate, int splits, void *workspace,
+                size_t workspace_bytes, const hsa_gemm_epilogue *epilogue, void *stream);
+int hsa_gemm_aborts(unsigned int *count);
+
+/*
  * Strided row copy between host and device (cudaMemcpy2DAsync on `stream`): `rows` rows of `row_bytes` bytes,
  * consecutive rows `src_pitch` / `dst_pitch` bytes apart.  kind: 0 = host to device, 1 = device to host,
  * 2 = device to device.  No counterpart in the reference (its tensors are created on the GPU); the host-side
@@ -237,6 +294,28 @@ int hsa_layer_norm_bwd(const void *x, const void *dy, const float *gamma, const 
  */
 int hsa_copy_rows_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t row_bytes,
                         size_t rows, int kind, void *stream);
+
+/* LayerNorm with float32 rows in and bfloat16 rows out (the normalised activations feed bfloat16 products), and its
+ * backward: bfloat16 upstream gradient, float32 input gradient dx = add + (gradient through the norm), `add` (NULL: none;
+ * may equal dx) being the gradient arriving through the residual connection around the branch
+ * (Hierarchical_Transformer_Pretrain.py:386,411,421). */
+int hsa_layer_norm_fwd_mixed(const float *x, const float *gamma, const float *beta, void *y_bf16, float *mean,
+                             float *rstd, int64_t rows, int d, float eps, void *stream);
+int hsa_layer_norm_bwd_mixed(const float *x, const void *dy_bf16, const float *gamma, const float *mean,
+                             const float *rstd, const float *add, float *dx, float *dgamma, float *dbeta,
+                             float *partial, int64_t rows, int d, void *stream);
+
+/*
+ * out[:, :, col_begin : col_begin+ncols] = keep ? in * scale : 0, as bfloat16, with the dropout masks of
+ * hsa_gemm_ex (same rng_state value, sites, threshold and element ids): the backward of a dropout that ran inside a
+ * product's epilogue.  `in` float32 or bfloat16 (in_dtype), `out` bfloat16; in == out (bfloat16) works in place.
+ * Column c of in / out counts as column c + col_shift of the logical tensor (a gradient buffer may hold the
+ * columns of several tensors side by side).
+ */
+int hsa_dropout_apply(hsa_view in, int in_dtype, hsa_view out, int batches, int rows, int col_begin, int ncols,
+                      long long N, long long rows_total, long long row_offset, long long col_shift,
+                      const unsigned long long *rng_state, unsigned int site0, unsigned int site1,
+                      unsigned int threshold, float scale, void *stream);
 
 /*
  * Span attention backward without any workspace argument.  No counterpart in the reference

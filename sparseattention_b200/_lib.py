@@ -28,6 +28,16 @@ class HsaError(RuntimeError):
     pass
 
 
+class GemmEpilogue(Structure):
+    """hsa_gemm_epilogue of include/hsa_b200.h."""
+    _fields_ = [("relu", c_int), ("rng_state", c_void_p), ("drop_site0", ctypes.c_uint), ("drop_site1", ctypes.c_uint),
+                ("drop_threshold", ctypes.c_uint), ("drop_scale", c_float), ("drop_col_begin", c_int),
+                ("drop_col_end", c_int), ("drop_rows_total", ctypes.c_longlong), ("drop_row_offset", ctypes.c_longlong),
+                ("gate", c_void_p), ("gate_bs", ctypes.c_longlong), ("gate_rs", ctypes.c_longlong), ("gate_scale", c_float),
+                ("residual", c_void_p), ("res_bs", ctypes.c_longlong), ("res_rs", ctypes.c_longlong),
+                ("copy_bf16", c_void_p), ("copy_bs", ctypes.c_longlong), ("copy_rs", ctypes.c_longlong)]
+
+
 # name -> (restype, argtypes); one entry per declaration in include/hsa_b200.h
 V = HsaView
 SIGNATURES = {
@@ -57,6 +67,15 @@ SIGNATURES = {
     "hsa_span_attn_logits": (c_int, [V, V, c_void_p] + [c_int] * 8 + [c_void_p]),
     "hsa_sibling_logits": (c_int, [V, V, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p]),
     "hsa_span_attn_decode": (c_int, [V, V, V, V] + [c_int] * 7 + [c_void_p]),
+    "hsa_gemm_workspace_bytes": (c_size_t, [c_int] * 7),
+    "hsa_gemm_choose_splits": (c_int, [c_int] * 4),
+    "hsa_gemm": (c_int, [V, V, V, c_void_p] + [c_int] * 9 + [c_void_p, c_size_t, c_void_p]),
+    "hsa_gemm_ex": (c_int, [V, V, V, c_void_p] + [c_int] * 9 + [c_void_p, c_size_t, c_void_p, c_void_p]),
+    "hsa_gemm_aborts": (c_int, [c_void_p]),
+    "hsa_layer_norm_fwd_mixed": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_float, c_void_p]),
+    "hsa_layer_norm_bwd_mixed": (c_int, [c_void_p] * 10 + [c_int64, c_int, c_void_p]),
+    "hsa_dropout_apply": (c_int, [V, c_int, V, c_int, c_int, c_int, c_int, ctypes.c_longlong, ctypes.c_longlong,
+                                  ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, c_float, c_void_p]),
     "hsa_copy_rows_async": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_size_t, c_size_t, c_int, c_void_p]),
     "hsa_span_attn_bwd_static": (c_int, [V, V, V, V, c_void_p, V, V, V, V] + [c_int] * 7 + [c_void_p]),
 }

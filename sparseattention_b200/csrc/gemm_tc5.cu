@@ -1,0 +1,514 @@
+// Dense bf16 / f16 matrix products on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor
+// memory), for the contractions of the attention layer and of the language model around it that share one dense
+// operand: the Q/K/V and output projections, the feed-forward pair and the LM head, forward and backward.
+//
+//   C[b, m, n] (+)= sum_k A[b, m, k] * B[n, k]  (+ bias[n])
+//
+// Persistent kernel, one CTA per SM, 6 warps with fixed roles:
+//   warp 0   producer: one thread issues the TMA tile loads of a stage (A box(es), B box(es)) onto its "full" mbarrier
+//   warp 1   one thread issues tcgen05.mma for the stage (four K=16 steps per 64-wide stage), commits the stage's
+//            "empty" mbarrier, and after the last stage of a tile commits the accumulator's "full" mbarrier;
+//            the warp also owns the tensor-memory allocation
+//   warps 2-5 epilogue: tcgen05.ld of the 128 x BN float32 accumulator (one row per thread), bias, conversion,
+//            16-byte global stores; two accumulators (2 x BN columns of tensor memory) alternate, so the epilogue of
+//            tile i overlaps the main loop of tile i+1
+// Operands sit in shared memory as 128-byte rows with the TMA unit's 128-byte swizzle, which is one of the
+// canonical tcgen05 operand layouts both for K-major tiles ([row][64 k]) and for MN-major tiles ([k][64 rows]);
+// so A and B may each be given as [rows, K] or transposed as [K, rows] without a transposing copy: the three
+// products of a linear layer (Y = X W^T, dX = dY W, dW = dY^T X) are the same kernel.
+// Long-K products with few output tiles (the weight gradients) are cut along K into `splits` pieces whose
+// float32 partial tiles are summed in a fixed order by a second kernel.
+// Every mbarrier wait is bounded; a CTA whose wait runs out raises a flag the other roles see, counts itself in
+// g_gemm_aborts (hsa_gemm_aborts reads it), frees its tensor memory and returns.
+#include <mutex>
+
+#include "hsa_common.cuh"
+#include "tc5_common.cuh"
+#include "rng_common.cuh"
+#include "tma_common.cuh"
+
+namespace hsa {
+
+constexpr int kBM = 128, kBK = 64;
+constexpr int kGemmThreads = 192;
+
+struct GemmArgs {
+    void *c;                      // [batches, rows, N] (OutT), element strides below
+    int64_t c_bs, c_rs;
+    const float *bias;            // [N] or null
+    float *partial;               // split-K: [splits, batches * m_tiles * 128, n_tiles * BN] float32, else null
+    int rows, batches, N;         // rows per batch of A and C
+    int k_blocks;                 // 64-wide K steps of the whole product
+    int kb_per_batch;             // A_MN / B_MN with batch-strided K: K steps per batch entry (k_blocks = batches * this)
+    int m_tiles, n_tiles, splits;
+    int accumulate;               // C += (float32 outputs only)
+    long long wait_limit;
+    hsa_gemm_epilogue epi;        // optional fused element-wise tail (all fields zero: none)
+};
+
+__device__ unsigned int g_gemm_aborts = 0;
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b) {
+    using namespace tc5;
+    constexpr int A_BYTES = kBM * 128, B_BYTES = BN * 128;
+    constexpr int STAGE = A_BYTES + B_BYTES;
+    constexpr int STAGES = BN == 256 ? 4 : 6;
+    constexpr uint32_t IDESC = instr_desc(kBM, BN, true, A_MN, B_MN);
+
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(smem + (size_t)STAGES * STAGE);
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t bar0 = smem_addr(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto acc_full = [&](int i) { return bar0 + 8u * (2 * STAGES + i); };
+    auto acc_empty = [&](int i) { return bar0 + 8u * (2 * STAGES + 2 + i); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(acc_full(i), 1); mbar_init(acc_empty(i), 4); }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_map(&map_a);
+        prefetch_map(&map_b);
+    }
+    if (warp == 1) tmem_alloc(smem_addr(tmem_slot), 2 * BN);
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_mn = a.m_tiles * a.n_tiles * a.batches;
+    const int total = tiles_mn * a.splits;
+    const int kb_split = (a.k_blocks + a.splits - 1) / a.splits;
+
+    // tile -> (split, batch, m tile, n tile); n fastest, so CTAs running together share A rows
+    auto decode = [&](int t, int &sp, int &b, int &mt, int &nt) {
+        nt = t % a.n_tiles; t /= a.n_tiles;
+        mt = t % a.m_tiles; t /= a.m_tiles;
+        b = t % a.batches;  sp = t / a.batches;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                int sp, b, mt, nt;
+                decode(t, sp, b, mt, nt);
+                const int kb0 = sp * kb_split, kb1 = min(a.k_blocks, kb0 + kb_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!(ok = mbar_wait(empty(s), ph ^ 1, a.wait_limit, abort_flag))) break;
+                    mbar_expect_tx(full(s), STAGE);
+                    const uint32_t sa = smem_addr(smem + (size_t)s * STAGE), sb = sa + A_BYTES;
+                    // K position of this step: a plain K offset, or (batch entry, row offset) when K runs over rows of a
+                    // batch-strided tensor
+                    const int kbatch = kb / a.kb_per_batch, krow = (kb % a.kb_per_batch) * kBK;
+                    if constexpr (!A_MN) {
+                        tma_load_3d(sa, &map_a, kb * kBK, mt * kBM, b, full(s));
+                    } else {
+#pragma unroll
+                        for (int p = 0; p < kBM / 64; ++p)
+                            tma_load_3d(sa + p * (kBK * 128), &map_a, mt * kBM + p * 64, krow, kbatch, full(s));
+                    }
+                    if constexpr (!B_MN) {
+                        tma_load_3d(sb, &map_b, kb * kBK, nt * BN, 0, full(s));
+                    } else {
+#pragma unroll
+                        for (int p = 0; p < BN / 64; ++p)
+                            tma_load_3d(sb + p * (kBK * 128), &map_b, nt * BN + p * 64, krow, kbatch, full(s));
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+            if (!ok) {                                   // let copies already issued land before the CTA goes
+                const long long t0 = clock64();
+                while (clock64() - t0 < 200000) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            int acc = 0; uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                int sp, b, mt, nt;
+                decode(t, sp, b, mt, nt);
+                const int kb0 = sp * kb_split, kb1 = min(a.k_blocks, kb0 + kb_split);
+                if (!(ok = mbar_wait(acc_empty(acc), acc_ph ^ 1, a.wait_limit, abort_flag))) break;
+                fence_after_sync();
+                const uint32_t d = tmem_base + acc * BN;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!(ok = mbar_wait(full(s), ph, a.wait_limit, abort_flag))) break;
+                    fence_after_sync();
+                    const uint32_t sa = smem_addr(smem + (size_t)s * STAGE), sb = sa + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        const uint64_t da = A_MN ? smem_desc(sa + k * 2048, kBK * 128, 1024) : smem_desc(sa + k * 32, 16, 1024);
+                        const uint64_t db = B_MN ? smem_desc(sb + k * 2048, kBK * 128, 1024) : smem_desc(sb + k * 32, 16, 1024);
+                        mma_f16(d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    mma_commit(empty(s));                 // the stage is free once these MMAs have read it
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                mma_commit(acc_full(acc));                // the accumulator is complete once all MMAs of the tile are
+                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;                            // the tensor-memory lane quarter this warp may read
+        int acc = 0; uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            int sp, b, mt, nt;
+            decode(t, sp, b, mt, nt);
+            ok = mbar_wait(acc_full(acc), acc_ph, a.wait_limit, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after_sync();
+            const int row = mt * kBM + q * 32 + lane;
+            const bool row_ok = row < a.rows;
+            const uint32_t tbase = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tbase + c0, r);
+                tmem_ld_wait();
+                const int col = nt * BN + c0;
+                if (a.partial != nullptr) {
+                    // split-K: the raw float32 tile goes to this split's slab (padded to whole tiles: no masks)
+                    float *dst = a.partial + ((size_t)sp * a.batches * a.m_tiles * kBM + ((size_t)b * a.m_tiles * kBM + row)) *
+                                                 ((size_t)a.n_tiles * BN) + col;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+                                                                          __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                } else if (row_ok && col < a.N) {
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    if (a.bias != nullptr) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            if (col + i < a.N) {
+                                const float4 bv = __ldg(reinterpret_cast<const float4 *>(a.bias + col + i));
+                                v[i] += bv.x; v[i + 1] += bv.y; v[i + 2] += bv.z; v[i + 3] += bv.w;
+                            }
+                        }
+                    }
+                    const hsa_gemm_epilogue &e = a.epi;
+                    if (e.relu) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+                    }
+                    if (e.rng_state != nullptr && col + 32 > e.drop_col_begin && col < e.drop_col_end) {
+                        // dropout on columns [drop_col_begin, drop_col_end): element id = (batch, row, column) of the logical
+                        // [batches, drop_rows_total, N] tensor this product writes a row range of
+                        const unsigned long long key = *e.rng_state;
+                        const unsigned long long id0 = ((unsigned long long)b * e.drop_rows_total + (unsigned long long)(row + e.drop_row_offset)) *
+                                                       (unsigned long long)a.N + (unsigned long long)col;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (col + i >= e.drop_col_begin && col + i < e.drop_col_end) {
+                                bool keep = dropout_keep(key, e.drop_site0, id0 + i, e.drop_threshold);
+                                if (e.drop_site1 != 0) keep = keep && dropout_keep(key, e.drop_site1, id0 + i, e.drop_threshold);
+                                v[i] = keep ? v[i] * e.drop_scale : 0.f;
+                            }
+                        }
+                    }
+                    if (e.gate != nullptr) {
+                        // pass the value where the gate tensor (same shape as the output) is positive: the backward of
+                        // relu followed by dropout, whose forward output is the gate
+                        const __nv_bfloat16 *gp = (const __nv_bfloat16 *)e.gate + b * e.gate_bs + (int64_t)row * e.gate_rs + col;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            if (col + i < a.N) {
+                                const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(gp + i));
+                                const __nv_bfloat16 *ge = reinterpret_cast<const __nv_bfloat16 *>(&raw);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[i + j] = (__bfloat162float(ge[j]) > 0.f) ? v[i + j] * e.gate_scale : 0.f;
+                            }
+                        }
+                    }
+                    if (e.residual != nullptr) {
+                        const float *rp = e.residual + b * e.res_bs + (int64_t)row * e.res_rs + col;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            if (col + i < a.N) {
+                                const float4 rv = __ldg(reinterpret_cast<const float4 *>(rp + i));
+                                v[i] += rv.x; v[i + 1] += rv.y; v[i + 2] += rv.z; v[i + 3] += rv.w;
+                            }
+                        }
+                    }
+                    OutT *dst = (OutT *)a.c + b * a.c_bs + (int64_t)row * a.c_rs + col;
+                    auto store_bf16 = [&](__nv_bfloat16 *d16) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            if (col + i < a.N) {
+                                uint4 o;
+                                __nv_bfloat162 *p = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                                *reinterpret_cast<uint4 *>(d16 + i) = o;
+                            }
+                        }
+                    };
+                    if constexpr (sizeof(OutT) == 2) {
+                        store_bf16(reinterpret_cast<__nv_bfloat16 *>(dst));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            if (col + i < a.N) {
+                                if (a.accumulate) {
+                                    const float4 old = *reinterpret_cast<const float4 *>(dst + i);
+                                    v[i] += old.x; v[i + 1] += old.y; v[i + 2] += old.z; v[i + 3] += old.w;
+                                }
+                                *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                            }
+                        }
+                        if (e.copy_bf16 != nullptr)
+                            store_bf16((__nv_bfloat16 *)e.copy_bf16 + b * e.copy_bs + (int64_t)row * e.copy_rs + col);
+                    }
+                }
+            }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(acc));
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) atomicAdd(&g_gemm_aborts, 1u);
+    if (warp == 1) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+}
+
+// Sum the split-K slabs in split order, add the bias, convert, store (one thread per four columns).
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+gemm_splitk_reduce_kernel(const float *__restrict__ partial, int splits, size_t slab, int rows, int batches, int N,
+                          int padded_rows, int padded_cols, OutT *c, int64_t c_bs, int64_t c_rs,
+                          const float *__restrict__ bias, int accumulate) {
+    const int cols4 = N / 4;
+    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= (size_t)batches * rows * cols4) return;
+    const int c4 = (int)(idx % cols4);
+    const size_t br = idx / cols4;
+    const int row = (int)(br % rows), b = (int)(br / rows);
+    const float *src = partial + ((size_t)b * padded_rows + row) * padded_cols + 4 * c4;
+    float4 s = *reinterpret_cast<const float4 *>(src);
+    for (int sp = 1; sp < splits; ++sp) {
+        const float4 v = *reinterpret_cast<const float4 *>(src + sp * slab);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    if (bias != nullptr) {
+        const float4 bv = *reinterpret_cast<const float4 *>(bias + 4 * c4);
+        s.x += bv.x; s.y += bv.y; s.z += bv.z; s.w += bv.w;
+    }
+    OutT *dst = c + b * c_bs + (int64_t)row * c_rs + 4 * c4;
+    if constexpr (sizeof(OutT) == 4) {
+        if (accumulate) {
+            const float4 old = *reinterpret_cast<const float4 *>(dst);
+            s.x += old.x; s.y += old.y; s.z += old.z; s.w += old.w;
+        }
+        *reinterpret_cast<float4 *>(dst) = s;
+    } else {
+        uint2 o;
+        __nv_bfloat162 *p = reinterpret_cast<__nv_bfloat162 *>(&o);
+        p[0] = __floats2bfloat162_rn(s.x, s.y);
+        p[1] = __floats2bfloat162_rn(s.z, s.w);
+        *reinterpret_cast<uint2 *>(dst) = o;
+    }
+}
+
+// A 3-D tensor map over 2-byte elements: dims {inner, rows, batches}, box {64, box_rows, 1}, 128-byte swizzle,
+// zero fill outside.
+static bool make_map3(CUtensorMap *m, const void *ptr, int64_t inner, int64_t rows, int64_t batches, int64_t row_stride,
+                      int64_t batch_stride, int box_rows) {
+    if (encode_tiled() == nullptr) return false;
+    if (batches == 1) batch_stride = rows * row_stride;
+    const cuuint64_t gdim[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)batches};
+    const cuuint64_t gstride[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)batch_stride * 2};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
+    const cuuint32_t estride[3] = {1u, 1u, 1u};
+    return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), gdim, gstride, box, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+        return v;
+    }();
+    return n;
+}
+
+}  // namespace hsa
+
+using namespace hsa;
+
+extern "C" int hsa_gemm_aborts(unsigned int *count) {
+    if (count == nullptr) return fail(HSA_ERR_ARG, "hsa_gemm_aborts: null pointer");
+    cudaError_t e = cudaMemcpyFromSymbol(count, g_gemm_aborts, sizeof(unsigned int));
+    return e == cudaSuccess ? 0 : fail((int)e, "hsa_gemm_aborts: %s", cudaGetErrorString(e));
+}
+
+extern "C" size_t hsa_gemm_workspace_bytes(int batches, int rows, int N, int K, int a_layout, int b_layout, int splits) {
+    (void)a_layout; (void)b_layout; (void)K;
+    if (splits <= 1 || batches < 1 || rows < 1 || N < 1) return 0;
+    const int BN = N > 128 ? 256 : 128;
+    const size_t m_tiles = (rows + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
+    return (size_t)splits * batches * m_tiles * kBM * n_tiles * BN * sizeof(float);
+}
+
+extern "C" int hsa_gemm_choose_splits(int batches, int rows, int N, int K) {
+    if (batches < 1 || rows < 1 || N < 1 || K < 1) return 1;
+    const int BN = N > 128 ? 256 : 128;
+    const long long tiles = (long long)batches * ((rows + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+    const int k_blocks = (K + kBK - 1) / kBK;
+    const int sms = sm_count();
+    if (tiles * 2 > sms || k_blocks < 16) return 1;
+    long long s = sms / tiles;
+    if (s > k_blocks / 4) s = k_blocks / 4;
+    return (int)(s < 1 ? 1 : s);
+}
+
+// Layout codes: 0 = the operand is stored [rows, K] (K contiguous); 1 = stored transposed, [K, rows].
+extern "C" int hsa_gemm(hsa_view A, hsa_view Bm, hsa_view C, const float *bias, int batches, int rows, int N, int K,
+                        int a_layout, int b_layout, int out_dtype, int accumulate, int splits, void *workspace,
+                        size_t workspace_bytes, void *stream) {
+    return hsa_gemm_ex(A, Bm, C, bias, batches, rows, N, K, a_layout, b_layout, out_dtype, accumulate, splits, workspace,
+                       workspace_bytes, nullptr, stream);
+}
+
+extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bias, int batches, int rows, int N, int K,
+                           int a_layout, int b_layout, int out_dtype, int accumulate, int splits, void *workspace,
+                           size_t workspace_bytes, const hsa_gemm_epilogue *epilogue, void *stream) {
+    HSA_CHECK_ARG(A.ptr && Bm.ptr && C.ptr, "hsa_gemm: null pointer");
+    HSA_CHECK_ARG(batches >= 1 && rows >= 1 && N >= 8 && K >= 1 && N % 8 == 0,
+                  "hsa_gemm: bad shape batches=%d rows=%d N=%d K=%d (N must be a multiple of 8)", batches, rows, N, K);
+    HSA_CHECK_ARG((a_layout | 1) == 1 && (b_layout | 1) == 1, "hsa_gemm: layout codes are 0 or 1");
+    HSA_CHECK_ARG(out_dtype == HSA_BF16 || out_dtype == HSA_F32, "hsa_gemm: the output is bfloat16 or float32");
+    HSA_CHECK_ARG(!accumulate || out_dtype == HSA_F32, "hsa_gemm: accumulation needs a float32 output");
+    HSA_CHECK_ARG(a_layout == 0 || rows % 8 == 0, "hsa_gemm: a transposed A needs rows %% 8 == 0");
+    HSA_CHECK_ARG(splits >= 1 && splits <= 1024, "hsa_gemm: splits out of range");
+    const int esz = out_dtype == HSA_F32 ? 4 : 2;
+    if (!aligned16(A.ptr) || !aligned16(Bm.ptr) || !aligned16(C.ptr) || (A.row_stride % 8) || (Bm.row_stride % 8) ||
+        (A.batch_stride % 8) || (C.row_stride * esz) % 16 || (C.batch_stride * esz) % 16 || (bias && !aligned16(bias)))
+        return fail(HSA_ERR_ALIGN, "hsa_gemm: pointers and strides must be 16-byte aligned");
+    const int BN = N > 128 ? 256 : 128;
+    GemmArgs g{};
+    g.c = C.ptr; g.c_bs = C.batch_stride; g.c_rs = C.row_stride; g.bias = bias;
+    g.rows = rows; g.batches = batches; g.N = N;
+    g.m_tiles = (rows + kBM - 1) / kBM;
+    g.n_tiles = (N + BN - 1) / BN;
+    g.accumulate = accumulate;
+    g.wait_limit = wait_limit_cycles();
+    if (epilogue != nullptr) {
+        g.epi = *epilogue;
+        const hsa_gemm_epilogue &e = g.epi;
+        HSA_CHECK_ARG(splits == 1, "hsa_gemm_ex: a fused epilogue needs splits == 1");
+        HSA_CHECK_ARG(a_layout == 0, "hsa_gemm_ex: a fused epilogue needs a_layout == 0");
+        HSA_CHECK_ARG(e.residual == nullptr || (aligned16(e.residual) && e.res_rs % 4 == 0 && e.res_bs % 4 == 0),
+                      "hsa_gemm_ex: residual must be 16-byte aligned");
+        HSA_CHECK_ARG(e.gate == nullptr || (aligned16(e.gate) && e.gate_rs % 8 == 0 && e.gate_bs % 8 == 0),
+                      "hsa_gemm_ex: gate must be 16-byte aligned");
+        HSA_CHECK_ARG(e.copy_bf16 == nullptr || (out_dtype == HSA_F32 && aligned16(e.copy_bf16) && e.copy_rs % 8 == 0 && e.copy_bs % 8 == 0),
+                      "hsa_gemm_ex: the bfloat16 copy needs a float32 main output and 16-byte alignment");
+        HSA_CHECK_ARG(e.rng_state == nullptr || (e.drop_col_begin >= 0 && e.drop_col_end <= N && e.drop_site0 != 0 && e.drop_rows_total >= rows),
+                      "hsa_gemm_ex: bad dropout description");
+    }
+    // K runs over rows of the stored tensors when an operand is transposed; a transposed A carries the batch dimension
+    // in K (the weight gradient sums over every row of every batch entry)
+    int out_batches = batches;
+    CUtensorMap ma, mb;
+    bool ok;
+    if (a_layout == 0) {
+        g.k_blocks = (K + kBK - 1) / kBK;
+        g.kb_per_batch = g.k_blocks;
+        ok = make_map3(&ma, A.ptr, K, rows, batches, A.row_stride, A.batch_stride, kBM);
+        // B: [N, K] or [K, N], shared by all batch entries
+        ok = ok && (b_layout == 0 ? make_map3(&mb, Bm.ptr, K, N, 1, Bm.row_stride, 0, BN)
+                                  : make_map3(&mb, Bm.ptr, N, K, 1, Bm.row_stride, 0, kBK));
+    } else {
+        // A stored [batches, K, rows]: C[rows, N] = sum over batch entries and k; B must be transposed as well,
+        // stored [batches, K, N], so both are cut along the same (batch entry, row) steps
+        HSA_CHECK_ARG(b_layout == 1, "hsa_gemm: a transposed A needs a transposed B ([K, N])");
+        g.kb_per_batch = (K + kBK - 1) / kBK;
+        g.k_blocks = g.kb_per_batch * batches;
+        out_batches = 1;
+        g.batches = 1;
+        ok = make_map3(&ma, A.ptr, rows, K, batches, A.row_stride, A.batch_stride, kBK) &&
+             make_map3(&mb, Bm.ptr, N, K, batches, Bm.row_stride, Bm.batch_stride, kBK);
+    }
+    if (!ok)
+        return fail(HSA_ERR_ARG,
+                    "hsa_gemm: the driver refused a tensor map (batches=%d rows=%d N=%d K=%d layouts %d/%d; A %p strides %lld/%lld; "
+                    "B %p strides %lld/%lld)", batches, rows, N, K, a_layout, b_layout, A.ptr, (long long)A.batch_stride,
+                    (long long)A.row_stride, Bm.ptr, (long long)Bm.batch_stride, (long long)Bm.row_stride);
+    if (splits > g.k_blocks) splits = g.k_blocks;
+    {   // every split must own at least one K step (an accumulator nobody wrote holds stale numbers)
+        const int per = (g.k_blocks + splits - 1) / splits;
+        splits = (g.k_blocks + per - 1) / per;
+    }
+    g.splits = splits;
+    if (splits > 1) {
+        const size_t need = hsa_gemm_workspace_bytes(out_batches, rows, N, K, a_layout, b_layout, splits);
+        if (workspace == nullptr || workspace_bytes < need)
+            return fail(HSA_ERR_WORKSPACE, "hsa_gemm: split-K workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+        if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(HSA_ERR_ALIGN, "hsa_gemm: workspace must be 256-byte aligned");
+        g.partial = (float *)workspace;
+    }
+    const long long total = (long long)g.m_tiles * g.n_tiles * g.batches * g.splits;
+    if (total > 0x7fffffffLL) return fail(HSA_ERR_ARG, "hsa_gemm: too many tiles");
+    const int grid = (int)(total < sm_count() ? total : sm_count());
+    cudaStream_t st = (cudaStream_t)stream;
+
+    auto launch = [&](auto kernel, int bn) -> int {
+        const int stages = bn == 256 ? 4 : 6;
+        const size_t smem = (size_t)stages * (kBM * 128 + bn * 128) + (2 * stages + 4) * 8 + 16 + 1024;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail((int)e, "hsa_gemm: shared memory %zu: %s", smem, cudaGetErrorString(e));
+        kernel<<<grid, kGemmThreads, smem, st>>>(g, ma, mb);
+        return launch_status("hsa_gemm");
+    };
+    int rc;
+#define HSA_GEMM_CASE(BNV, AMN, BMN)                                                                     \
+    (out_dtype == HSA_F32 || g.partial ? launch(gemm_tc5_kernel<BNV, AMN, BMN, float>, BNV)               \
+                                       : launch(gemm_tc5_kernel<BNV, AMN, BMN, __nv_bfloat16>, BNV))
+    if (BN == 256) {
+        rc = a_layout ? HSA_GEMM_CASE(256, true, true) : (b_layout ? HSA_GEMM_CASE(256, false, true) : HSA_GEMM_CASE(256, false, false));
+    } else {
+        rc = a_layout ? HSA_GEMM_CASE(128, true, true) : (b_layout ? HSA_GEMM_CASE(128, false, true) : HSA_GEMM_CASE(128, false, false));
+    }
+#undef HSA_GEMM_CASE
+    if (rc != 0 || splits == 1) return rc;
+    const size_t slab = (size_t)out_batches * g.m_tiles * kBM * g.n_tiles * BN;
+    const size_t work = (size_t)out_batches * rows * (N / 4);
+    const unsigned blocks = (unsigned)((work + 255) / 256);
+    if (out_dtype == HSA_F32)
+        gemm_splitk_reduce_kernel<float><<<blocks, 256, 0, st>>>(g.partial, splits, slab, rows, out_batches, N, g.m_tiles * kBM,
+                                                                 g.n_tiles * BN, (float *)C.ptr, C.batch_stride, C.row_stride, bias, accumulate);
+    else
+        gemm_splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(g.partial, splits, slab, rows, out_batches, N, g.m_tiles * kBM,
+                                                                         g.n_tiles * BN, (__nv_bfloat16 *)C.ptr, C.batch_stride,
+                                                                         C.row_stride, bias, 0);
+    return launch_status("hsa_gemm(split-K reduce)");
+}

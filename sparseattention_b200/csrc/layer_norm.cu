@@ -38,10 +38,10 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // lane l owns columns 4*(l + 32*i) .. +3 for i < NV (consecutive lanes read consecutive 16-byte pieces)
-template <typename T, int NV>
+template <typename T, int NV, typename TY = T>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layer_norm_fwd_kernel(const T *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
-                      T *__restrict__ y, float *__restrict__ mean, float *__restrict__ rstd, int64_t rows, float eps) {
+                      TY *__restrict__ y, float *__restrict__ mean, float *__restrict__ rstd, int64_t rows, float eps) {
     constexpr int d = 128 * NV;
     const int lane = threadIdx.x & 31;
     const int64_t warps = (int64_t)gridDim.x * kLnWarps;
@@ -72,17 +72,17 @@ layer_norm_fwd_kernel(const T *__restrict__ x, const float *__restrict__ gamma, 
             float4 o;
             o.x = v[i].x * rs * g[i].x + bt[i].x; o.y = v[i].y * rs * g[i].y + bt[i].y;
             o.z = v[i].z * rs * g[i].z + bt[i].z; o.w = v[i].w * rs * g[i].w + bt[i].w;
-            ln_store4<T>(y + r * d + 4 * (lane + 32 * i), o);
+            ln_store4<TY>(y + r * d + 4 * (lane + 32 * i), o);
         }
         if (lane == 0) { mean[r] = mu; rstd[r] = rs; }
     }
 }
 
-template <typename T, int NV>
+template <typename T, int NV, typename TY = T>
 __global__ void __launch_bounds__(kLnWarps * 32)
-layer_norm_bwd_kernel(const T *__restrict__ x, const T *__restrict__ dy, const float *__restrict__ gamma,
-                      const float *__restrict__ mean, const float *__restrict__ rstd, T *__restrict__ dx,
-                      float *__restrict__ partial /* [gridDim.x][2][d] */, int64_t rows) {
+layer_norm_bwd_kernel(const T *__restrict__ x, const TY *__restrict__ dy, const float *__restrict__ gamma,
+                      const float *__restrict__ mean, const float *__restrict__ rstd, T *dx,
+                      float *__restrict__ partial /* [gridDim.x][2][d] */, int64_t rows, const T *add = nullptr) {
     constexpr int d = 128 * NV;
     __shared__ float4 red[kLnWarps][2][NV][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -101,7 +101,7 @@ layer_norm_bwd_kernel(const T *__restrict__ x, const T *__restrict__ dy, const f
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const float4 xv = ln_load4<T>(x + r * d + 4 * (lane + 32 * i));
-            const float4 dv = ln_load4<T>(dy + r * d + 4 * (lane + 32 * i));
+            const float4 dv = ln_load4<TY>(dy + r * d + 4 * (lane + 32 * i));
             xh[i] = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
             gy[i] = make_float4(dv.x * g[i].x, dv.y * g[i].y, dv.z * g[i].z, dv.w * g[i].w);
             s1 += gy[i].x + gy[i].y + gy[i].z + gy[i].w;
@@ -115,6 +115,10 @@ layer_norm_bwd_kernel(const T *__restrict__ x, const T *__restrict__ dy, const f
             float4 o;
             o.x = rs * (gy[i].x - m1 - xh[i].x * m2); o.y = rs * (gy[i].y - m1 - xh[i].y * m2);
             o.z = rs * (gy[i].z - m1 - xh[i].z * m2); o.w = rs * (gy[i].w - m1 - xh[i].w * m2);
+            if (add != nullptr) {                                 // the gradient arriving through the residual connection
+                const float4 old = ln_load4<T>(add + r * d + 4 * (lane + 32 * i));
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
             ln_store4<T>(dx + r * d + 4 * (lane + 32 * i), o);
         }
     }
@@ -226,4 +230,42 @@ extern "C" int hsa_layer_norm_bwd(const void *x, const void *dy, const float *ga
         if (!ok) return fail(HSA_ERR_ARG, "hsa_layer_norm_bwd: width %d not supported (128, 256, 384, 512, 768)", d);
         return rc;
     });
+}
+
+// float32 rows in, bfloat16 rows out (the normalised activations feed bfloat16 products), and the matching backward:
+// bfloat16 upstream gradient, float32 gradient of the input, optionally ADDED to what dx already holds (the gradient
+// arriving through the residual connection around the normalised branch).
+extern "C" int hsa_layer_norm_fwd_mixed(const float *x, const float *gamma, const float *beta, void *y_bf16, float *mean,
+                                        float *rstd, int64_t rows, int d, float eps, void *stream) {
+    HSA_CHECK_ARG(x && gamma && beta && y_bf16 && mean && rstd, "hsa_layer_norm_fwd_mixed: null pointer");
+    HSA_CHECK_ARG(rows >= 1, "hsa_layer_norm_fwd_mixed: rows=%lld", (long long)rows);
+    HSA_CHECK_ARG(aligned16(x) && aligned16(y_bf16) && aligned16(gamma) && aligned16(beta), "hsa_layer_norm_fwd_mixed: pointers must be 16-byte aligned");
+    int rc = 0;
+    const bool ok = ln_dispatch_width(d, [&]<int NV>() {
+        layer_norm_fwd_kernel<float, NV, __nv_bfloat16><<<ln_grid(rows), kLnWarps * 32, 0, (cudaStream_t)stream>>>(
+            x, gamma, beta, (__nv_bfloat16 *)y_bf16, mean, rstd, rows, eps);
+        rc = launch_status("hsa_layer_norm_fwd_mixed");
+    });
+    if (!ok) return fail(HSA_ERR_ARG, "hsa_layer_norm_fwd_mixed: width %d not supported (128, 256, 384, 512, 768)", d);
+    return rc;
+}
+
+extern "C" int hsa_layer_norm_bwd_mixed(const float *x, const void *dy_bf16, const float *gamma, const float *mean,
+                                        const float *rstd, const float *add, float *dx, float *dgamma, float *dbeta,
+                                        float *partial, int64_t rows, int d, void *stream) {
+    HSA_CHECK_ARG(x && dy_bf16 && gamma && mean && rstd && dx && dgamma && dbeta && partial, "hsa_layer_norm_bwd_mixed: null pointer");
+    HSA_CHECK_ARG(rows >= 1, "hsa_layer_norm_bwd_mixed: rows=%lld", (long long)rows);
+    HSA_CHECK_ARG(aligned16(x) && aligned16(dy_bf16) && aligned16(dx) && aligned16(gamma) && aligned16(partial) && aligned16(add),
+                  "hsa_layer_norm_bwd_mixed: pointers must be 16-byte aligned");
+    int rc = 0;
+    const int ctas = ln_grid(rows);
+    const bool ok = ln_dispatch_width(d, [&]<int NV>() {
+        layer_norm_bwd_kernel<float, NV, __nv_bfloat16><<<ctas, kLnWarps * 32, 0, (cudaStream_t)stream>>>(
+            x, (const __nv_bfloat16 *)dy_bf16, gamma, mean, rstd, dx, partial, rows, add);
+        if ((rc = launch_status("hsa_layer_norm_bwd_mixed"))) return;
+        layer_norm_bwd_reduce_kernel<<<(2 * d + 31) / 32, 256, 0, (cudaStream_t)stream>>>(partial, dgamma, dbeta, ctas, d);
+        rc = launch_status("hsa_layer_norm_bwd_mixed(reduce)");
+    });
+    if (!ok) return fail(HSA_ERR_ARG, "hsa_layer_norm_bwd_mixed: width %d not supported (128, 256, 384, 512, 768)", d);
+    return rc;
 }

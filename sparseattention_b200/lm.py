@@ -73,8 +73,14 @@ class DecoderLayer(nn.Module):
         self.norm2 = norm_cls(d_model)
         self.norm_y = norm_cls(d_model)
         self.dropout = nn.Dropout(dropout)
+        self.fused = True           # set False to force the eager path (the numerical reference of the fused one)
 
     def forward(self, x, y, mask=None, return_attention: bool = False):
+        if self.fused and not return_attention and type(self.self_attn) is HierarchicalAttention:
+            from .fused_layer import fused_decoder_layer, fused_layer_supported
+            if fused_layer_supported(self, x, y, mask):
+                # bf16 autocast on CUDA: the whole layer as one autograd node (tcgen05 products with fused tails)
+                return fused_decoder_layer(self, x, y, mask)
         y_delta = self.self_attn.cross_update_Y(x, y_in=self.norm_y(y))
         y_next = y + self.dropout(y_delta)
         norm_x = self.norm1(x)

@@ -342,6 +342,231 @@ def test_span_attention_full_size_properties(hsa):
     assert rel_err(lse[:, sample].cpu(), torch.logsumexp(logits, dim=-1)) < 1e-4
 
 
+# ------------------------------------------------------------------------------------- tcgen05 products
+GEMM_CASES = [
+    # batches, rows, N, K
+    (1, 128, 256, 64), (1, 128, 128, 64), (1, 256, 512, 512), (1, 100, 256, 72), (2, 200, 520, 136), (3, 64, 64, 512),
+    (1, 1000, 1536, 512), (1, 384, 50304, 512), (4, 33, 1024, 2048), (1, 4096, 512, 2048), (1, 8, 8, 8),
+]
+
+
+def _gemm_inputs(batches, rows, N, K, seed):
+    gen = torch.Generator().manual_seed(seed)
+    A = torch.randn(batches, rows, K, generator=gen).bfloat16()
+    W = torch.randn(N, K, generator=gen).bfloat16()
+    bias = torch.randn(N, generator=gen)
+    return A, W, bias
+
+
+@pytest.mark.parametrize("case", GEMM_CASES)
+def test_gemm_forward_product(hsa, case):
+    """C = A W^T (+ bias) on the tcgen05 kernel against a float64 product of the same bf16 operands."""
+    from sparseattention_b200.ops.gemm import gemm, gemm_aborts
+    batches, rows, N, K = case
+    A, W, bias = _gemm_inputs(*case, seed=rows + N)
+    want = torch.einsum("brk,nk->brn", A.double(), W.double())
+    got = gemm(A.cuda(), W.cuda(), out_dtype=torch.float32)
+    assert rel_err(got.cpu(), want) < 1e-5
+    got = gemm(A.cuda(), W.cuda(), bias=bias.cuda())
+    assert got.dtype == torch.bfloat16 and rel_err(got.float().cpu(), want + bias.double()) < 1e-2
+    # operands and result as strided views of wider tensors; a forced split along K
+    wideA = torch.zeros(batches, rows + 3, K + 16, dtype=torch.bfloat16, device="cuda")
+    wideA[:, 1:rows + 1, 8:K + 8] = A.cuda()
+    wideC = torch.full((batches, rows, N + 24), 7.0, dtype=torch.float32, device="cuda")
+    gemm(wideA[:, 1:rows + 1, 8:K + 8], W.cuda(), out=wideC[:, :, 8:N + 8], splits=2 if K >= 128 else 1)
+    assert rel_err(wideC[:, :, 8:N + 8].cpu(), want) < 1e-5
+    assert float((wideC[:, :, :8] - 7).abs().max()) == 0 and float((wideC[:, :, N + 8:] - 7).abs().max()) == 0
+    assert gemm_aborts() == 0
+
+
+@pytest.mark.parametrize("case", GEMM_CASES)
+def test_gemm_transposed_operands(hsa, case):
+    """The two backward products of a linear layer: dX = dY W (B read as [K, N]) and dW = dY^T X summed over all batch
+    entries (both operands read transposed), with automatic and forced split-K; accumulation into float32."""
+    from sparseattention_b200.ops.gemm import gemm, gemm_aborts
+    batches, rows, N, K = case
+    A, W, _ = _gemm_inputs(*case, seed=rows * 3 + K)
+    gen = torch.Generator().manual_seed(N)
+    dY = torch.randn(batches, rows, N, generator=gen).bfloat16()
+    want_dx = torch.einsum("brn,nk->brk", dY.double(), W.double())
+    got = gemm(dY.cuda(), W.cuda(), b_t=True, out_dtype=torch.float32)
+    assert rel_err(got.cpu(), want_dx) < 1e-5
+    if K % 8 == 0:
+        want_dw = torch.einsum("brn,brk->nk", dY.double(), A.double())
+        for splits in (None, 1, 3):
+            got = gemm(dY.cuda(), A.cuda(), a_t=True, b_t=True, out_dtype=torch.float32, splits=splits)
+            assert got.shape == (N, K) and rel_err(got.cpu(), want_dw) < 1e-5, splits
+        acc = torch.ones(N, K, device="cuda")
+        gemm(dY.cuda(), A.cuda(), a_t=True, b_t=True, out=acc, accumulate=True)
+        assert rel_err(acc.cpu(), want_dw + 1) < 1e-5
+    assert gemm_aborts() == 0
+
+
+def test_linear_matches_torch(hsa):
+    """ops.gemm.linear against F.linear in float64 on the bf16-rounded operands: output and the three gradients."""
+    from sparseattention_b200.ops.gemm import linear
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn(4, 300, 512, generator=gen).bfloat16()
+    w = torch.randn(1024, 512, generator=gen) * 0.05
+    b = torch.randn(1024, generator=gen)
+    gy = torch.randn(4, 300, 1024, generator=gen).bfloat16()
+    xr, wr, br = x.double().requires_grad_(), w.bfloat16().double().requires_grad_(), b.double().requires_grad_()
+    torch.nn.functional.linear(xr, wr, br).backward(gy.double())
+    xc, wc, bc = x.cuda().requires_grad_(), w.cuda().requires_grad_(), b.cuda().requires_grad_()
+    y = linear(xc, wc, bc)
+    y.backward(gy.cuda())
+    assert y.dtype == torch.bfloat16 and rel_err(y.detach().float().cpu(), torch.nn.functional.linear(xr, wr, br).detach()) < 1e-2
+    assert xc.grad.dtype == torch.bfloat16 and rel_err(xc.grad.float().cpu(), xr.grad) < 1e-2
+    assert wc.grad.dtype == torch.float32 and rel_err(wc.grad.cpu(), wr.grad) < 1e-4
+    assert rel_err(bc.grad.cpu(), br.grad) < 1e-4
+
+
+def test_gemm_fused_tails(hsa):
+    """The element-wise tails of hsa_gemm_ex against the same steps done by hand: bias + relu, residual, bfloat16 copy,
+    gate; and dropout inside the epilogue against the plain product followed by hsa_dropout_apply (which must
+    regenerate exactly the same masks: that is what the backward relies on)."""
+    from sparseattention_b200.ops.gemm import DropoutSpec, gemm
+    gen = torch.Generator().manual_seed(5)
+    B, rows, N, K = 2, 300, 512, 256
+    A = torch.randn(B, rows, K, generator=gen).bfloat16().cuda()
+    W = (torch.randn(N, K, generator=gen) * 0.1).bfloat16().cuda()
+    bias = torch.randn(N, generator=gen).cuda()
+    res = torch.randn(B, rows, N, generator=gen).cuda()
+    plain = gemm(A, W, out_dtype=torch.float32)
+    got = gemm(A, W, bias=bias, relu=True, out_dtype=torch.float32)
+    assert rel_err(got.cpu(), torch.relu(plain + bias).cpu()) < 1e-6
+    copy = torch.empty(B, rows, N, dtype=torch.bfloat16, device="cuda")
+    got = gemm(A, W, bias=bias, out=torch.empty_like(res), residual=res, copy_bf16=copy)
+    assert rel_err(got.cpu(), (plain + bias + res).cpu()) < 1e-6 and torch.equal(copy, got.bfloat16())
+    gate = torch.randn(B, rows, N, generator=gen).bfloat16().cuda()
+    got = gemm(A, W, out_dtype=torch.float32, gate=gate, gate_scale=1.25)
+    assert rel_err(got.cpu(), torch.where(gate > 0, plain * 1.25, torch.zeros_like(plain)).cpu()) < 1e-6
+    # dropout: epilogue == product, then apply; one and two masks, a column range, rows of a larger logical tensor
+    key = torch.tensor([1234567], dtype=torch.int64, device="cuda")
+    for site1 in (0, 9):
+        spec = DropoutSpec(key, 0.1, 3, site1)
+        want = gemm(A, W)
+        spec.apply(want, want, 256, 256, N, 1000, 17)
+        got = gemm(A, W, dropout=spec, drop_cols=(256, 512), drop_rows_total=1000, drop_row_offset=17)
+        assert torch.equal(got == 0, want == 0)                   # the same elements are dropped ...
+        assert rel_err(got.float().cpu(), want.float().cpu()) < 1e-2   # ... and the kept ones agree up to one more bf16 rounding
+        kept = float((got[..., 256:] != 0).float().mean())
+        assert abs(kept - (0.9 ** (2 if site1 else 1))) < 0.01
+        assert torch.equal(got[..., :256], gemm(A, W)[..., :256])
+        ratio = got[..., 256:].float() / gemm(A, W)[..., 256:].float()
+        scale = 1 / 0.9 ** (2 if site1 else 1)
+        assert float((ratio[got[..., 256:] != 0] - scale).abs().max()) < 0.02
+    # another key gives another mask; float32 input converts on the way; shifted columns
+    spec = DropoutSpec(key, 0.1, 3)
+    a = spec.apply(plain, torch.empty_like(plain, dtype=torch.bfloat16), 0, N, N, rows)
+    b2 = DropoutSpec(key + 1, 0.1, 3).apply(plain, torch.empty_like(plain, dtype=torch.bfloat16), 0, N, N, rows)
+    assert not torch.equal(a, b2)
+    wide = torch.zeros(B, rows, 2 * N, dtype=torch.bfloat16, device="cuda")
+    wide[..., N:] = plain.bfloat16()
+    spec.apply(wide, wide, N, N, N, rows, 0, -N)
+    assert torch.equal(wide[..., N:] == 0, a == 0) and rel_err(wide[..., N:].float().cpu(), a.float().cpu()) < 1e-2
+
+
+@pytest.mark.parametrize("shape", [(2, 256, 256, 4, 512), (1, 1024, 512, 8, 2048), (3, 128, 128, 2, 256)])
+def test_fused_decoder_layer_against_eager(hsa, shape):
+    """The one-node decoder layer (tcgen05 products, fused tails, hand-written backward) under bf16 autocast: both
+    outputs, both input gradients and every parameter gradient, no dropout.  The yardstick is the eager layer in
+    float32 (Linear weights rounded to bfloat16, as autocast rounds them); the bound for each tensor is 2e-2, or,
+    where bfloat16 itself costs more than that (the relu gate of the feed-forward flips for pre-activations near
+    zero, which moves fc1's and norm2's gradients by several percent in ANY bf16 run), 1.25 x the error of the
+    eager bf16-autocast layer on the same inputs."""
+    import copy
+    from sparseattention_b200.fused_layer import fused_layer_supported
+    from sparseattention_b200.lm import DecoderLayer
+    torch.backends.cuda.matmul.allow_tf32 = False
+    B, N, d, H, ff = shape
+    torch.manual_seed(N + d)
+    layer = DecoderLayer(d, H, ff, dropout=0.0, window_size=16).cuda().train()
+    with torch.no_grad():
+        for prm in layer.parameters():                       # biases and norm parameters away from their trivial values
+            if prm.dim() == 1:
+                prm.add_(torch.randn_like(prm) * 0.1)
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(B, N, d, generator=gen).cuda()
+    y = torch.randn(B, N - 1, d, generator=gen).cuda()
+    gx = torch.randn(B, N, d, generator=gen).cuda()
+    gy = torch.randn(B, N - 1, d, generator=gen).cuda()
+    ref = copy.deepcopy(layer).float()
+    ref.fused = False
+    with torch.no_grad():
+        for mod in ref.modules():
+            if isinstance(mod, torch.nn.Linear):
+                mod.weight.copy_(mod.weight.bfloat16().float())
+    flag = torch.ones(1, device="cuda")
+
+    def run(mod, autocast):
+        for prm in mod.parameters():
+            prm.grad = None
+        xr, yr = x.clone().requires_grad_(), y.clone().requires_grad_()
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+            if autocast and mod.fused:
+                assert fused_layer_supported(mod, xr, yr, flag)
+            xo, yo = mod(xr, yr, mask=flag)
+        ((xo * gx).sum() + (yo * gy).sum()).backward()
+        out = {"x_out": xo.detach(), "y_out": yo.detach(), "dx": xr.grad, "dy": yr.grad}
+        for name, prm in mod.named_parameters():
+            assert prm.grad is not None, name
+            out[name] = prm.grad.clone()
+        return {k: v.float().cpu() for k, v in out.items()}
+
+    want = run(ref, False)
+    layer.fused = True
+    fused = run(layer, True)
+    layer.fused = False
+    eager = run(layer, True)
+    assert fused["x_out"].dtype == torch.float32
+    for name in want:
+        bound = max(2e-2, 1.25 * rel_err(eager[name], want[name]))
+        assert rel_err(fused[name], want[name]) < bound, name
+
+
+def test_fused_decoder_layer_dropout(hsa):
+    """With dropout the fused layer draws a new mask per call, yet forward and backward of one call agree on it: the
+    layer is linear in the feed-forward output bias, so the gradient of sum(x_out) for that bias must equal the
+    per-column sum of the kept-and-scaled mask, which the forward exposes as x_out(b2 + 1) - x_out(b2)."""
+    from sparseattention_b200.lm import DecoderLayer
+    torch.manual_seed(1)
+    B, N, d, H, ff = 2, 256, 256, 4, 512
+    layer = DecoderLayer(d, H, ff, dropout=0.1, window_size=16).cuda().train()
+    x = torch.randn(B, N, d, device="cuda")
+    y = torch.randn(B, N - 1, d, device="cuda")
+    flag = torch.ones(1, device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        a, _ = layer(x, y, mask=flag)
+        b2, _ = layer(x, y, mask=flag)
+    assert bool(torch.isfinite(a).all()) and not torch.equal(a, b2)
+    layer.eval()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        e1, _ = layer(x, y, mask=flag)
+        e2, _ = layer(x, y, mask=flag)
+    assert torch.equal(e1, e2)
+    assert rel_err(a.cpu(), e1.cpu()) < 0.5 and rel_err(a.cpu(), e1.cpu()) > 1e-3
+    # same key: same masks, forward and backward
+    import sparseattention_b200.fused_layer as fl
+    layer.train()
+    cfg = {"heads": H, "window": 16, "causal": True, "p": 0.1, "eps": 1e-5}
+    key = torch.tensor([99], dtype=torch.int64, device="cuda")
+    prm = list(fl.fused_layer_parameters(layer))
+    xg = x.clone().requires_grad_()
+    out1, _ = fl.FusedDecoderLayerFunction.apply(xg, y, cfg, key, *prm)
+    out1.sum().backward()
+    grad_b2 = layer.feed_forward.fc2.bias.grad.clone()
+    with torch.no_grad():
+        prm2 = list(prm)
+        prm2[-1] = prm[-1] + 1.0
+        out2, _ = fl.FusedDecoderLayerFunction.apply(x, y, cfg, key, *prm2)
+        out3, _ = fl.FusedDecoderLayerFunction.apply(x, y, cfg, key, *prm)
+    assert torch.equal(out3, out1.detach())
+    mask_colsum = (out2 - out1.detach()).sum(dim=(0, 1))
+    assert rel_err(grad_b2.cpu(), mask_colsum.cpu()) < 5e-3      # 1/(1-p) is rounded to bfloat16 in the backward's operand
+    assert abs(float(mask_colsum.mean()) / (B * N) - 1.0) < 0.02
+
+
 # ------------------------------------------------------------------------------------- logits ops
 def test_logits_ops_golden(hsa, golden):
     """Span-attention weights against the tensor the reference's forward saves; the first prototype's cross logits
