@@ -4,14 +4,15 @@
 //
 //   C[b, m, n] (+)= sum_k A[b, m, k] * B[n, k]  (+ bias[n])
 //
-// Persistent kernel, one CTA per SM, 6 warps with fixed roles:
+// Persistent kernel, one CTA per SM, 10 warps with fixed roles:
 //   warp 0   producer: one thread issues the TMA tile loads of a stage (A box(es), B box(es)) onto its "full" mbarrier
 //   warp 1   one thread issues tcgen05.mma for the stage (four K=16 steps per 64-wide stage), commits the stage's
 //            "empty" mbarrier, and after the last stage of a tile commits the accumulator's "full" mbarrier;
 //            the warp also owns the tensor-memory allocation
-//   warps 2-5 epilogue: tcgen05.ld of the 128 x BN float32 accumulator (one row per thread), bias, conversion,
-//            16-byte global stores; two accumulators (2 x BN columns of tensor memory) alternate, so the epilogue of
-//            tile i overlaps the main loop of tile i+1
+//   warps 2-9 epilogue: tcgen05.ld of the 128 x BN float32 accumulator (a thread owns one row and half of its
+//            columns), bias and the fused tail, conversion, 16-byte global stores; two accumulators (2 x BN columns of
+//            tensor memory) alternate, so the epilogue of tile i overlaps the main loop of tile i+1.  With the short
+//            reductions of this model (K = 512: 2.9 us of MMA per tile) four epilogue warps could not keep up
 // Operands sit in shared memory as 128-byte rows with the TMA unit's 128-byte swizzle, which is one of the
 // canonical tcgen05 operand layouts both for K-major tiles ([row][64 k]) and for MN-major tiles ([k][64 rows]);
 // so A and B may each be given as [rows, K] or transposed as [K, rows] without a transposing copy: the three
@@ -30,7 +31,8 @@
 namespace hsa {
 
 constexpr int kBM = 128, kBK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;                      // two warps per tensor-memory lane quarter, half the columns each
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 
 struct GemmArgs {
     void *c;                      // [batches, rows, N] (OutT), element strides below
@@ -40,26 +42,37 @@ struct GemmArgs {
     int rows, batches, N;         // rows per batch of A and C
     int k_blocks;                 // 64-wide K steps of the whole product
     int kb_per_batch;             // A_MN / B_MN with batch-strided K: K steps per batch entry (k_blocks = batches * this)
-    int m_tiles, n_tiles, splits;
+    int m_tiles, n_tiles, splits; // m tiles of 128 rows (one CTA per tile) or 256 rows (a CTA pair per tile)
     int accumulate;               // C += (float32 outputs only)
+    int tma_store;                // output rows leave through the copy engine (needs map_c; not with accumulate / split-K)
     long long wait_limit;
     hsa_gemm_epilogue epi;        // optional fused element-wise tail (all fields zero: none)
 };
 
 __device__ unsigned int g_gemm_aborts = 0;
 
-template <int BN, bool A_MN, bool B_MN, typename OutT>
+// TWO: the tile is 256 x BN and belongs to a pair of CTAs (cluster of two, tcgen05 cta_group::2): each CTA stages its
+// own 128 rows of A and half of the B tile, so a stage is 32 KB instead of 48 KB per 128 output rows and every byte
+// fetched from L2 feeds twice the arithmetic.  With this model's short reductions (K = 512) the single-CTA form is
+// bound by L2 bandwidth (85 flop per byte staged), not by the tensor pipe.
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool TWO>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b) {
+gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_c) {
     using namespace tc5;
-    constexpr int A_BYTES = kBM * 128, B_BYTES = BN * 128;
+    constexpr int B_ROWS = TWO ? BN / 2 : BN;          // rows of the B tile this CTA stages
+    constexpr int MT = TWO ? 2 * kBM : kBM;            // rows of a tile
+    constexpr int A_BYTES = kBM * 128, B_BYTES = B_ROWS * 128;
     constexpr int STAGE = A_BYTES + B_BYTES;
-    constexpr int STAGES = BN == 256 ? 4 : 6;
-    constexpr uint32_t IDESC = instr_desc(kBM, BN, true, A_MN, B_MN);
+    constexpr int STAGES = STAGE == 49152 ? 4 : 6;
+    constexpr uint32_t IDESC = instr_desc(MT, BN, true, A_MN, B_MN);
+    const uint32_t rank = TWO ? cluster_ctarank() : 0;  // 0 = the CTA that issues the MMAs
+    const int unit = TWO ? blockIdx.x / 2 : blockIdx.x, nunits = TWO ? gridDim.x / 2 : gridDim.x;
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
-    unsigned long long *bars = reinterpret_cast<unsigned long long *>(smem + (size_t)STAGES * STAGE);
+    unsigned char *staging = smem + (size_t)STAGES * STAGE;           // 2 x 16 KB: one block of output rows per column half
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(staging + 32768);
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -72,15 +85,20 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(acc_full(i), 1); mbar_init(acc_empty(i), 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(acc_full(i), 1); mbar_init(acc_empty(i), (TWO ? 2 : 1) * kEpiWarps); }
         *abort_flag = 0;
         mbar_fence_init();
         prefetch_map(&map_a);
         prefetch_map(&map_b);
+        if (a.tma_store) prefetch_map(&map_c);
     }
-    if (warp == 1) tmem_alloc(smem_addr(tmem_slot), 2 * BN);
+    if (warp == 1) {
+        if constexpr (TWO) tmem_alloc_pair(smem_addr(tmem_slot), 2 * BN);
+        else tmem_alloc(smem_addr(tmem_slot), 2 * BN);
+    }
     fence_before_sync();
     __syncthreads();
+    if constexpr (TWO) cluster_sync();                 // the partner's barriers exist before anything signals them
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -100,30 +118,35 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            // in a pair both CTAs' copies are counted on the even CTA's "full" barrier, which expects both stages
+            auto load = [&](uint32_t dst, const CUtensorMap *map, int x0, int y0, int z0, uint32_t mb) {
+                if constexpr (TWO) tma_load_3d_pair(dst, map, x0, y0, z0, mb);
+                else tma_load_3d(dst, map, x0, y0, z0, mb);
+            };
+            for (int t = unit; t < total && ok; t += nunits) {
                 int sp, b, mt, nt;
                 decode(t, sp, b, mt, nt);
                 const int kb0 = sp * kb_split, kb1 = min(a.k_blocks, kb0 + kb_split);
+                const int m0 = mt * MT + (int)rank * kBM, n0 = nt * BN + (int)rank * B_ROWS;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!(ok = mbar_wait(empty(s), ph ^ 1, a.wait_limit, abort_flag))) break;
-                    mbar_expect_tx(full(s), STAGE);
+                    if (rank == 0) mbar_expect_tx(full(s), (TWO ? 2 : 1) * STAGE);
+                    const uint32_t fb = TWO ? map_to_cta(full(s), 0) : full(s);
                     const uint32_t sa = smem_addr(smem + (size_t)s * STAGE), sb = sa + A_BYTES;
                     // K position of this step: a plain K offset, or (batch entry, row offset) when K runs over rows of a
                     // batch-strided tensor
                     const int kbatch = kb / a.kb_per_batch, krow = (kb % a.kb_per_batch) * kBK;
                     if constexpr (!A_MN) {
-                        tma_load_3d(sa, &map_a, kb * kBK, mt * kBM, b, full(s));
+                        load(sa, &map_a, kb * kBK, m0, b, fb);
                     } else {
 #pragma unroll
-                        for (int p = 0; p < kBM / 64; ++p)
-                            tma_load_3d(sa + p * (kBK * 128), &map_a, mt * kBM + p * 64, krow, kbatch, full(s));
+                        for (int p = 0; p < kBM / 64; ++p) load(sa + p * (kBK * 128), &map_a, m0 + p * 64, krow, kbatch, fb);
                     }
                     if constexpr (!B_MN) {
-                        tma_load_3d(sb, &map_b, kb * kBK, nt * BN, 0, full(s));
+                        load(sb, &map_b, kb * kBK, n0, 0, fb);
                     } else {
 #pragma unroll
-                        for (int p = 0; p < BN / 64; ++p)
-                            tma_load_3d(sb + p * (kBK * 128), &map_b, nt * BN + p * 64, krow, kbatch, full(s));
+                        for (int p = 0; p < B_ROWS / 64; ++p) load(sb + p * (kBK * 128), &map_b, n0 + p * 64, krow, kbatch, fb);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -135,11 +158,11 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issue
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             int s = 0; uint32_t ph = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            for (int t = unit; t < total && ok; t += nunits) {
                 int sp, b, mt, nt;
                 decode(t, sp, b, mt, nt);
                 const int kb0 = sp * kb_split, kb1 = min(a.k_blocks, kb0 + kb_split);
@@ -154,49 +177,65 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                     for (int k = 0; k < kBK / 16; ++k) {
                         const uint64_t da = A_MN ? smem_desc(sa + k * 2048, kBK * 128, 1024) : smem_desc(sa + k * 32, 16, 1024);
                         const uint64_t db = B_MN ? smem_desc(sb + k * 2048, kBK * 128, 1024) : smem_desc(sb + k * 32, 16, 1024);
-                        mma_f16(d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+                        if constexpr (TWO) mma_f16_pair(d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+                        else mma_f16(d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
-                    mma_commit(empty(s));                 // the stage is free once these MMAs have read it
+                    // the stage is free (in both CTAs of a pair) once these MMAs have read it
+                    if constexpr (TWO) mma_commit_pair(empty(s)); else mma_commit(empty(s));
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (!ok) break;
-                mma_commit(acc_full(acc));                // the accumulator is complete once all MMAs of the tile are
+                // the accumulator is complete once all MMAs of the tile are
+                if constexpr (TWO) mma_commit_pair(acc_full(acc)); else mma_commit(acc_full(acc));
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
         }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int q = warp & 3;                            // the tensor-memory lane quarter this warp may read
+        const int col_lo = ((warp - 2) >> 2) * (BN / 2);   // ... and the half of the tile's columns it owns
         int acc = 0; uint32_t acc_ph = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        for (int t = unit; t < total && ok; t += nunits) {
             int sp, b, mt, nt;
             decode(t, sp, b, mt, nt);
             ok = mbar_wait(acc_full(acc), acc_ph, a.wait_limit, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
+            {   // the four warps that share a staging block go on (or give up) together
+                uint32_t all_ok;
+                asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.and.pred p, %2, 128, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+                             : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1 + ((warp - 2) >> 2)) : "memory");
+                ok = all_ok != 0;
+            }
             if (!ok) break;
             fence_after_sync();
-            const int row = mt * kBM + q * 32 + lane;
+            const int row = mt * MT + (int)rank * kBM + q * 32 + lane;
             const bool row_ok = row < a.rows;
             const uint32_t tbase = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+            const int half = (warp - 2) >> 2;                 // which half of the tile's columns
+            const int row_local = q * 32 + lane;              // row inside this CTA's 128 rows
+            unsigned char *stg = staging + half * 16384;      // [128 rows][128 B], 128-byte swizzle, for the TMA stores
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = col_lo; c0 < col_lo + BN / 2; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tbase + c0, r);
                 tmem_ld_wait();
                 const int col = nt * BN + c0;
                 if (a.partial != nullptr) {
                     // split-K: the raw float32 tile goes to this split's slab (padded to whole tiles: no masks)
-                    float *dst = a.partial + ((size_t)sp * a.batches * a.m_tiles * kBM + ((size_t)b * a.m_tiles * kBM + row)) *
+                    float *dst = a.partial + ((size_t)sp * a.batches * a.m_tiles * MT + ((size_t)b * a.m_tiles * MT + row)) *
                                                  ((size_t)a.n_tiles * BN) + col;
 #pragma unroll
                     for (int i = 0; i < 32; i += 4)
                         *reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
                                                                           __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-                } else if (row_ok && col < a.N) {
-                    float v[32];
+                    continue;
+                }
+                const bool live = row_ok && col < a.N;        // dead rows / columns still take part in the staged store
+                float v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                const hsa_gemm_epilogue &e = a.epi;
+                if (live) {
                     if (a.bias != nullptr) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
@@ -206,7 +245,6 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                             }
                         }
                     }
-                    const hsa_gemm_epilogue &e = a.epi;
                     if (e.relu) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
@@ -250,19 +288,60 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                             }
                         }
                     }
-                    OutT *dst = (OutT *)a.c + b * a.c_bs + (int64_t)row * a.c_rs + col;
-                    auto store_bf16 = [&](__nv_bfloat16 *d16) {
+                }
+                OutT *dst = (OutT *)a.c + b * a.c_bs + (int64_t)row * a.c_rs + col;
+                auto store_bf16 = [&](__nv_bfloat16 *d16) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            if (col + i < a.N) {
-                                uint4 o;
-                                __nv_bfloat162 *p = reinterpret_cast<__nv_bfloat162 *>(&o);
+                    for (int i = 0; i < 32; i += 8) {
+                        if (col + i < a.N) {
+                            uint4 o;
+                            __nv_bfloat162 *p = reinterpret_cast<__nv_bfloat162 *>(&o);
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
-                                *reinterpret_cast<uint4 *>(d16 + i) = o;
-                            }
+                            for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                            *reinterpret_cast<uint4 *>(d16 + i) = o;
                         }
-                    };
+                    }
+                };
+                if (a.tma_store) {
+                    // Rows leave through the copy engine: the 4 warps of this half park a [128 rows][128 B] block in shared
+                    // memory (swizzled like the tensor map expects) and one thread stores it with a single bulk copy, which
+                    // writes whole lines and clips what lies outside the tensor.  Per-thread 16-byte stores would touch half
+                    // a sector each.
+                    constexpr int CPG = sizeof(OutT) == 2 ? 64 : 32;          // columns per 128-byte staged row
+                    const int cg = (c0 - col_lo) % CPG;                       // first column of this chunk inside the group
+                    unsigned char *srow = stg + row_local * 128;
+                    if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 o;
+                            __nv_bfloat162 *p = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+                            *reinterpret_cast<uint4 *>(srow + (((cg / 8 + i) ^ (row_local & 7)) << 4)) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<float4 *>(srow + ((i ^ (row_local & 7)) << 4)) =
+                                make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    }
+                    if (cg + 32 == CPG) {                                     // the group is complete: hand it to the copy engine
+                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
+                        if (q == 0 && lane == 0) {
+                            const int gcol = nt * BN + c0 + 32 - CPG;
+                            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];\n"
+                                         ::"l"(&map_c), "r"(gcol), "r"(mt * MT + (int)rank * kBM), "r"(b), "r"(smem_addr(stg)) : "memory");
+                            asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                            asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+                        }
+                        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
+                    }
+                    if constexpr (sizeof(OutT) == 4) {
+                        if (live && e.copy_bf16 != nullptr)
+                            store_bf16((__nv_bfloat16 *)e.copy_bf16 + b * e.copy_bs + (int64_t)row * e.copy_rs + col);
+                    }
+                } else if (live) {
                     if constexpr (sizeof(OutT) == 2) {
                         store_bf16(reinterpret_cast<__nv_bfloat16 *>(dst));
                     } else {
@@ -283,17 +362,23 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
             }
             fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty(acc));
+            if (lane == 0) {                                  // the MMA thread (even CTA of a pair) may reuse the accumulator
+                if constexpr (TWO) mbar_arrive_cluster(map_to_cta(acc_empty(acc), 0));
+                else mbar_arrive(acc_empty(acc));
+            }
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
     }
 
     // ---------------------------------------------------------------------- teardown
+    fence_before_sync();
     __syncthreads();
+    if constexpr (TWO) cluster_sync();                 // nobody leaves while the partner may still touch its memory
     if (*abort_flag && threadIdx.x == 0) atomicAdd(&g_gemm_aborts, 1u);
     if (warp == 1) {
         fence_after_sync();
-        tmem_dealloc(tmem_base, 2 * BN);
+        if constexpr (TWO) tmem_dealloc_pair(tmem_base, 2 * BN);
+        else tmem_dealloc(tmem_base, 2 * BN);
     }
 }
 
@@ -335,6 +420,8 @@ gemm_splitk_reduce_kernel(const float *__restrict__ partial, int splits, size_t 
     }
 }
 
+static thread_local int g_last_map_result = 0;      // CUresult of the last cuTensorMapEncodeTiled, for error messages
+
 // A 3-D tensor map over 2-byte elements: dims {inner, rows, batches}, box {64, box_rows, 1}, 128-byte swizzle,
 // zero fill outside.
 static bool make_map3(CUtensorMap *m, const void *ptr, int64_t inner, int64_t rows, int64_t batches, int64_t row_stride,
@@ -345,9 +432,25 @@ static bool make_map3(CUtensorMap *m, const void *ptr, int64_t inner, int64_t ro
     const cuuint64_t gstride[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)batch_stride * 2};
     const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
     const cuuint32_t estride[3] = {1u, 1u, 1u};
-    return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), gdim, gstride, box, estride,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const CUresult r = encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), gdim, gstride, box, estride,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    g_last_map_result = (int)r;
+    return r == CUDA_SUCCESS;
+}
+
+// The output tensor [batches, rows, N] for bulk stores of [128 rows][128 bytes] blocks.
+static bool make_map_out(CUtensorMap *m, const void *ptr, int64_t N, int64_t rows, int64_t batches, int64_t row_stride,
+                         int64_t batch_stride, int esize) {
+    if (encode_tiled() == nullptr) return false;
+    if (batches == 1) batch_stride = rows * row_stride;
+    const cuuint64_t gdim[3] = {(cuuint64_t)N, (cuuint64_t)rows, (cuuint64_t)batches};
+    const cuuint64_t gstride[2] = {(cuuint64_t)row_stride * esize, (cuuint64_t)batch_stride * esize};
+    const cuuint32_t box[3] = {(cuuint32_t)(128 / esize), 128u, 1u};
+    const cuuint32_t estride[3] = {1u, 1u, 1u};
+    return encode_tiled()(m, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                          const_cast<void *>(ptr), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 static int sm_count() {
@@ -370,22 +473,33 @@ extern "C" int hsa_gemm_aborts(unsigned int *count) {
     return e == cudaSuccess ? 0 : fail((int)e, "hsa_gemm_aborts: %s", cudaGetErrorString(e));
 }
 
+// Tile shape of a product: BN = 256 columns (128 for narrow outputs); 256-row tiles on CTA pairs when a batch entry
+// has at least 256 rows, else 128-row tiles on single CTAs.
+struct GemmShape { int BN, MT; bool two; };
+static GemmShape gemm_shape(int rows, int N) {
+    GemmShape s;
+    s.BN = N > 128 ? 256 : 128;
+    s.two = rows >= 256;
+    s.MT = s.two ? 2 * kBM : kBM;
+    return s;
+}
+
 extern "C" size_t hsa_gemm_workspace_bytes(int batches, int rows, int N, int K, int a_layout, int b_layout, int splits) {
     (void)a_layout; (void)b_layout; (void)K;
     if (splits <= 1 || batches < 1 || rows < 1 || N < 1) return 0;
-    const int BN = N > 128 ? 256 : 128;
-    const size_t m_tiles = (rows + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
-    return (size_t)splits * batches * m_tiles * kBM * n_tiles * BN * sizeof(float);
+    const GemmShape sh = gemm_shape(rows, N);
+    const size_t m_tiles = (rows + sh.MT - 1) / sh.MT, n_tiles = (N + sh.BN - 1) / sh.BN;
+    return (size_t)splits * batches * m_tiles * sh.MT * n_tiles * sh.BN * sizeof(float);
 }
 
 extern "C" int hsa_gemm_choose_splits(int batches, int rows, int N, int K) {
     if (batches < 1 || rows < 1 || N < 1 || K < 1) return 1;
-    const int BN = N > 128 ? 256 : 128;
-    const long long tiles = (long long)batches * ((rows + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+    const GemmShape sh = gemm_shape(rows, N);
+    const long long tiles = (long long)batches * ((rows + sh.MT - 1) / sh.MT) * ((N + sh.BN - 1) / sh.BN);
     const int k_blocks = (K + kBK - 1) / kBK;
-    const int sms = sm_count();
-    if (tiles * 2 > sms || k_blocks < 16) return 1;
-    long long s = sms / tiles;
+    const int units = sh.two ? sm_count() / 2 : sm_count();        // tiles that run at once
+    if (tiles * 2 > units || k_blocks < 16) return 1;
+    long long s = units / tiles;
     if (s > k_blocks / 4) s = k_blocks / 4;
     return (int)(s < 1 ? 1 : s);
 }
@@ -413,11 +527,12 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
     if (!aligned16(A.ptr) || !aligned16(Bm.ptr) || !aligned16(C.ptr) || (A.row_stride % 8) || (Bm.row_stride % 8) ||
         (A.batch_stride % 8) || (C.row_stride * esz) % 16 || (C.batch_stride * esz) % 16 || (bias && !aligned16(bias)))
         return fail(HSA_ERR_ALIGN, "hsa_gemm: pointers and strides must be 16-byte aligned");
-    const int BN = N > 128 ? 256 : 128;
+    const GemmShape sh = gemm_shape(rows, N);
+    const int BN = sh.BN;
     GemmArgs g{};
     g.c = C.ptr; g.c_bs = C.batch_stride; g.c_rs = C.row_stride; g.bias = bias;
     g.rows = rows; g.batches = batches; g.N = N;
-    g.m_tiles = (rows + kBM - 1) / kBM;
+    g.m_tiles = (rows + sh.MT - 1) / sh.MT;
     g.n_tiles = (N + BN - 1) / BN;
     g.accumulate = accumulate;
     g.wait_limit = wait_limit_cycles();
@@ -445,7 +560,7 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
         g.kb_per_batch = g.k_blocks;
         ok = make_map3(&ma, A.ptr, K, rows, batches, A.row_stride, A.batch_stride, kBM);
         // B: [N, K] or [K, N], shared by all batch entries
-        ok = ok && (b_layout == 0 ? make_map3(&mb, Bm.ptr, K, N, 1, Bm.row_stride, 0, BN)
+        ok = ok && (b_layout == 0 ? make_map3(&mb, Bm.ptr, K, N, 1, Bm.row_stride, 0, sh.two ? BN / 2 : BN)
                                   : make_map3(&mb, Bm.ptr, N, K, 1, Bm.row_stride, 0, kBK));
     } else {
         // A stored [batches, K, rows]: C[rows, N] = sum over batch entries and k; B must be transposed as well,
@@ -460,8 +575,8 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
     }
     if (!ok)
         return fail(HSA_ERR_ARG,
-                    "hsa_gemm: the driver refused a tensor map (batches=%d rows=%d N=%d K=%d layouts %d/%d; A %p strides %lld/%lld; "
-                    "B %p strides %lld/%lld)", batches, rows, N, K, a_layout, b_layout, A.ptr, (long long)A.batch_stride,
+                    "hsa_gemm: the driver refused a tensor map, CUresult %d (batches=%d rows=%d N=%d K=%d layouts %d/%d; A %p strides %lld/%lld; "
+                    "B %p strides %lld/%lld)", g_last_map_result, batches, rows, N, K, a_layout, b_layout, A.ptr, (long long)A.batch_stride,
                     (long long)A.row_stride, Bm.ptr, (long long)Bm.batch_stride, (long long)Bm.row_stride);
     if (splits > g.k_blocks) splits = g.k_blocks;
     {   // every split must own at least one K step (an accumulator nobody wrote holds stale numbers)
@@ -476,23 +591,46 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
         if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(HSA_ERR_ALIGN, "hsa_gemm: workspace must be 256-byte aligned");
         g.partial = (float *)workspace;
     }
+    // the output's tensor map (rows leave by bulk copies), unless the epilogue has to read C back or writes partial slabs
+    CUtensorMap mc = ma;
+    g.tma_store = 0;
+    if (g.partial == nullptr && !accumulate && make_map_out(&mc, C.ptr, N, rows, out_batches, C.row_stride, C.batch_stride, esz))
+        g.tma_store = 1;
     const long long total = (long long)g.m_tiles * g.n_tiles * g.batches * g.splits;
     if (total > 0x7fffffffLL) return fail(HSA_ERR_ARG, "hsa_gemm: too many tiles");
-    const int grid = (int)(total < sm_count() ? total : sm_count());
+    const int units = sh.two ? sm_count() / 2 : sm_count();
+    const int grid = (int)(total < units ? total : units) * (sh.two ? 2 : 1);
     cudaStream_t st = (cudaStream_t)stream;
 
     auto launch = [&](auto kernel, int bn) -> int {
-        const int stages = bn == 256 ? 4 : 6;
-        const size_t smem = (size_t)stages * (kBM * 128 + bn * 128) + (2 * stages + 4) * 8 + 16 + 1024;
+        const int stage = kBM * 128 + (sh.two ? bn / 2 : bn) * 128;
+        const int stages = stage == 49152 ? 4 : 6;
+        const size_t smem = (size_t)stages * stage + 32768 + (2 * stages + 4) * 8 + 16 + 1024;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "hsa_gemm: shared memory %zu: %s", smem, cudaGetErrorString(e));
-        kernel<<<grid, kGemmThreads, smem, st>>>(g, ma, mb);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = sh.two ? 2 : 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, kernel, g, ma, mb, mc);
+        if (e != cudaSuccess) return fail((int)e, "hsa_gemm: launch: %s", cudaGetErrorString(e));
         return launch_status("hsa_gemm");
     };
+    const bool f32 = out_dtype == HSA_F32 || g.partial != nullptr;
     int rc;
-#define HSA_GEMM_CASE(BNV, AMN, BMN)                                                                     \
-    (out_dtype == HSA_F32 || g.partial ? launch(gemm_tc5_kernel<BNV, AMN, BMN, float>, BNV)               \
-                                       : launch(gemm_tc5_kernel<BNV, AMN, BMN, __nv_bfloat16>, BNV))
+#define HSA_GEMM_CASE(BNV, AMN, BMN)                                                                                   \
+    (sh.two ? (f32 ? launch(gemm_tc5_kernel<BNV, AMN, BMN, float, true>, BNV)                                          \
+                   : launch(gemm_tc5_kernel<BNV, AMN, BMN, __nv_bfloat16, true>, BNV))                                 \
+            : (f32 ? launch(gemm_tc5_kernel<BNV, AMN, BMN, float, false>, BNV)                                         \
+                   : launch(gemm_tc5_kernel<BNV, AMN, BMN, __nv_bfloat16, false>, BNV)))
     if (BN == 256) {
         rc = a_layout ? HSA_GEMM_CASE(256, true, true) : (b_layout ? HSA_GEMM_CASE(256, false, true) : HSA_GEMM_CASE(256, false, false));
     } else {
@@ -500,14 +638,14 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
     }
 #undef HSA_GEMM_CASE
     if (rc != 0 || splits == 1) return rc;
-    const size_t slab = (size_t)out_batches * g.m_tiles * kBM * g.n_tiles * BN;
+    const size_t slab = (size_t)out_batches * g.m_tiles * sh.MT * g.n_tiles * BN;
     const size_t work = (size_t)out_batches * rows * (N / 4);
     const unsigned blocks = (unsigned)((work + 255) / 256);
     if (out_dtype == HSA_F32)
-        gemm_splitk_reduce_kernel<float><<<blocks, 256, 0, st>>>(g.partial, splits, slab, rows, out_batches, N, g.m_tiles * kBM,
+        gemm_splitk_reduce_kernel<float><<<blocks, 256, 0, st>>>(g.partial, splits, slab, rows, out_batches, N, g.m_tiles * sh.MT,
                                                                  g.n_tiles * BN, (float *)C.ptr, C.batch_stride, C.row_stride, bias, accumulate);
     else
-        gemm_splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(g.partial, splits, slab, rows, out_batches, N, g.m_tiles * kBM,
+        gemm_splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(g.partial, splits, slab, rows, out_batches, N, g.m_tiles * sh.MT,
                                                                          g.n_tiles * BN, (__nv_bfloat16 *)C.ptr, C.batch_stride,
                                                                          C.row_stride, bias, 0);
     return launch_status("hsa_gemm(split-K reduce)");

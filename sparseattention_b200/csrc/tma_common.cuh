@@ -14,6 +14,14 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline EncodeTiledFn encode_tiled() {
+    // cuTensorMapEncodeTiled is a driver-API call: it needs a context current on the calling thread.  The runtime binds
+    // one lazily, so on a thread whose first CUDA call this is (an autograd worker running a backward, for one) it would
+    // fail with CUDA_ERROR_INVALID_CONTEXT; cudaFree(0) makes the runtime bind the device's primary context.
+    thread_local bool bound = false;
+    if (!bound) {
+        cudaFree(nullptr);
+        bound = true;
+    }
     static EncodeTiledFn fn = [] {
         void *p = nullptr;
         cudaDriverEntryPointQueryResult q;
