@@ -97,6 +97,37 @@ int hsa_parent_nodes_bwd(hsa_view dOut, hsa_view Qp, hsa_view Kp, hsa_view Vp, h
                          hsa_view dVc, int B, int P, int H, int D, int dtype, void *stream);
 
 /*
+ * The bottom-up refresh above level `start_level` as one launch per tree, forward and backward.  Replaces the level
+ * loop of HierarchicalAttention.cross_update_Y (hierarchical_attention/modules/attention.py:128-157: per level a
+ * projection of the previous level's output with Wk_y / Wv_y, dropout of the values, the parent kernel) and of its
+ * autograd backward; the reference's author notes the launch problem at ops/triton/build_parents.py:207-216.
+ *   Qp, Kp, Vp : [B, N-1, H*D] projections of all parents (level l = rows N - N/2^l ..), bfloat16, any row stride
+ *   R          : [B, N-1, H*D] refreshed parents; rows of levels < start_level must be there, the rest is written
+ *   KVc        : [B, N-1, 2*H*D] child projections [K | V] of every non-root row of R (row r of KVc = projection of
+ *                row r of R); rows of levels < start_level - 1 must be there (their parents run outside), the rest is written
+ *   Wkv        : [2*H*D, H*D] bfloat16 contiguous, Wk_y stacked on Wv_y
+ *   dropout    : rng_state NULL = none; else the value half of KVc is masked with site / threshold / drop_scale and
+ *                element ids of the [B, N-1, 2*H*D] tensor (hsa_dropout_apply / hsa_gemm_ex regenerate the same masks)
+ * Backward: dRf [B, N-1, H*D] float32 holds the gradient of R on entry (from the output projection) and dRb its bfloat16
+ *   copy; both are updated in place level by level; dQp, dKp, dVp rows of levels >= start_level and dKVc rows of levels
+ *   >= start_level - 1 are written (value half already masked).  The weight gradient dKVc^T R is left to the caller
+ *   (one product over all levels).
+ * The launch is cooperative (one CTA per SM, all resident); CTAs meet at a counter in `state` (hsa_parent_tree_state_bytes
+ * bytes of device memory, cleared by the call) and wait there at most the library's wait limit; a CTA that gives up writes
+ * a non-zero status that makes all others leave.  hsa_parent_tree_status reads it (0 = every level completed); it
+ * synchronises.  H*D a multiple of 256, D 64 or 128, 1 <= start_level < log2 N.
+ */
+size_t hsa_parent_tree_state_bytes(void);
+int hsa_parent_tree_status(const void *state, unsigned int *status);
+int hsa_parent_tree_fwd(hsa_view Qp, hsa_view Kp, hsa_view Vp, hsa_view R, hsa_view KVc, const void *Wkv, int B, int N,
+                        int H, int D, int start_level, const unsigned long long *rng_state, unsigned int site,
+                        unsigned int threshold, float drop_scale, void *state, void *stream);
+int hsa_parent_tree_bwd(hsa_view Qp, hsa_view Kp, hsa_view Vp, hsa_view KVc, hsa_view dRf, hsa_view dRb, hsa_view dQp,
+                        hsa_view dKp, hsa_view dVp, hsa_view dKVc, const void *Wkv, int B, int N, int H, int D,
+                        int start_level, const unsigned long long *rng_state, unsigned int site,
+                        unsigned int threshold, float drop_scale, void *state, void *stream);
+
+/*
  * Span attention forward.  Replaces hierarchical_attention /
  * HierarchicalAttentionFunc.forward (ops/functional.py:114-168,274;
  * ops/triton/sparse_attn.py:8-179).
@@ -272,6 +303,11 @@ typedef struct hsa_gemm_epilogue {
     const void *gate; long long gate_bs, gate_rs; float gate_scale;
     const float *residual; long long res_bs, res_rs;
     void *copy_bf16; long long copy_bs, copy_rs;
+    /* Cross-entropy statistics of the (bfloat16) output taken as logits: see hsa_linear_ce_combine. */
+    float *ce_partial;            /* [batches * rows, 2 * column tiles, 4] float32; NULL = none */
+    const long long *ce_targets;  /* [batches * rows] int64 */
+    int ce_classes;               /* columns >= ce_classes are padding, not classes */
+    int ce_skip_store;            /* != 0: do not write the logits at all (loss only) */
 } hsa_gemm_epilogue;
 
 size_t hsa_gemm_workspace_bytes(int batches, int rows, int N, int K, int a_layout, int b_layout, int splits);
@@ -283,6 +319,19 @@ int hsa_gemm_ex(hsa_view A, hsa_view B, hsa_view C, const float *bias, int batch
                 int a_layout, int b_layout, int out_dtype, int accumulate, int splits, void *workspace,
                 size_t workspace_bytes, const hsa_gemm_epilogue *epilogue, void *stream);
 int hsa_gemm_aborts(unsigned int *count);
+
+/*
+ * LM head and loss in one pass: the reference computes logits = fc_out(x) and then nn.CrossEntropyLoss(label_smoothing)
+ * over the [tokens, vocabulary] matrix (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.py:480,514,562-572),
+ * reading the logits again.  Here the product's epilogue (hsa_gemm_ex with ce_partial set) keeps, per row and per half
+ * column tile, the running (max, sum of exponentials, sum, target logit) of the logits it has in registers;
+ * hsa_linear_ce_combine merges them into loss_rows[r] and lse[r] (same definitions as hsa_cross_entropy_fwd).  With
+ * ce_skip_store the logits are never written (evaluation); for training they are stored once for the backward
+ * (hsa_cross_entropy_bwd, which may overwrite them in place).  ce_partial holds hsa_linear_ce_partial_bytes(rows, N) bytes.
+ */
+size_t hsa_linear_ce_partial_bytes(long long rows, int N);
+int hsa_linear_ce_combine(const float *partial, long long rows, int N, const long long *targets, float *loss_rows,
+                          float *lse, int classes, float smoothing, long long ignore_index, void *stream);
 
 /*
  * Strided row copy between host and device (cudaMemcpy2DAsync on `stream`): `rows` rows of `row_bytes` bytes,

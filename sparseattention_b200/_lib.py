@@ -35,7 +35,8 @@ class GemmEpilogue(Structure):
                 ("drop_col_end", c_int), ("drop_rows_total", ctypes.c_longlong), ("drop_row_offset", ctypes.c_longlong),
                 ("gate", c_void_p), ("gate_bs", ctypes.c_longlong), ("gate_rs", ctypes.c_longlong), ("gate_scale", c_float),
                 ("residual", c_void_p), ("res_bs", ctypes.c_longlong), ("res_rs", ctypes.c_longlong),
-                ("copy_bf16", c_void_p), ("copy_bs", ctypes.c_longlong), ("copy_rs", ctypes.c_longlong)]
+                ("copy_bf16", c_void_p), ("copy_bs", ctypes.c_longlong), ("copy_rs", ctypes.c_longlong),
+                ("ce_partial", c_void_p), ("ce_targets", c_void_p), ("ce_classes", c_int), ("ce_skip_store", c_int)]
 
 
 # name -> (restype, argtypes); one entry per declaration in include/hsa_b200.h
@@ -50,6 +51,12 @@ SIGNATURES = {
     "hsa_span_input_y_bwd": (c_int, [V, V, c_int, c_int, c_int, c_int, c_void_p]),
     "hsa_parent_nodes_fwd": (c_int, [V, V, V, V, V, V, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "hsa_parent_nodes_bwd": (c_int, [V] * 11 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "hsa_parent_tree_state_bytes": (c_size_t, []),
+    "hsa_parent_tree_status": (c_int, [c_void_p, c_void_p]),
+    "hsa_parent_tree_fwd": (c_int, [V, V, V, V, V, c_void_p] + [c_int] * 5 + [c_void_p, ctypes.c_uint, ctypes.c_uint, c_float,
+                                    c_void_p, c_void_p]),
+    "hsa_parent_tree_bwd": (c_int, [V] * 10 + [c_void_p] + [c_int] * 5 + [c_void_p, ctypes.c_uint, ctypes.c_uint, c_float,
+                                    c_void_p, c_void_p]),
     "hsa_span_attn_fwd": (c_int, [V, V, V, V, c_void_p] + [c_int] * 8 + [c_void_p]),
     "hsa_span_attn_fwd_wait_expired": (c_int, [c_void_p]),
     "hsa_debug_wait_test": (c_int, [ctypes.c_longlong, ctypes.c_uint]),
@@ -72,6 +79,9 @@ SIGNATURES = {
     "hsa_gemm": (c_int, [V, V, V, c_void_p] + [c_int] * 9 + [c_void_p, c_size_t, c_void_p]),
     "hsa_gemm_ex": (c_int, [V, V, V, c_void_p] + [c_int] * 9 + [c_void_p, c_size_t, c_void_p, c_void_p]),
     "hsa_gemm_aborts": (c_int, [c_void_p]),
+    "hsa_linear_ce_partial_bytes": (c_size_t, [ctypes.c_longlong, c_int]),
+    "hsa_linear_ce_combine": (c_int, [c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float,
+                                      ctypes.c_longlong, c_void_p]),
     "hsa_layer_norm_fwd_mixed": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_float, c_void_p]),
     "hsa_layer_norm_bwd_mixed": (c_int, [c_void_p] * 10 + [c_int64, c_int, c_void_p]),
     "hsa_dropout_apply": (c_int, [V, c_int, V, c_int, c_int, c_int, c_int, ctypes.c_longlong, ctypes.c_longlong,

@@ -211,6 +211,10 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
             const int row = mt * MT + (int)rank * kBM + q * 32 + lane;
             const bool row_ok = row < a.rows;
             const uint32_t tbase = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+            // cross-entropy statistics of this thread's row over its half of the tile's columns (when asked for)
+            float ce_m = -INFINITY, ce_s = 0.f, ce_sx = 0.f, ce_xt = 0.f;
+            long long ce_target = -1;
+            if (a.epi.ce_partial != nullptr && row_ok) ce_target = a.epi.ce_targets[(long long)b * a.rows + row];
             const int half = (warp - 2) >> 2;                 // which half of the tile's columns
             const int row_local = q * 32 + lane;              // row inside this CTA's 128 rows
             unsigned char *stg = staging + half * 16384;      // [128 rows][128 B], 128-byte swizzle, for the TMA stores
@@ -264,29 +268,94 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                             }
                         }
                     }
-                    if (e.gate != nullptr) {
-                        // pass the value where the gate tensor (same shape as the output) is positive: the backward of
-                        // relu followed by dropout, whose forward output is the gate
-                        const __nv_bfloat16 *gp = (const __nv_bfloat16 *)e.gate + b * e.gate_bs + (int64_t)row * e.gate_rs + col;
+                }
+                // Gate and residual blocks are fetched by the four warps of this half together, 8 threads per 128-byte row
+                // (whole lines, like the output block leaves), through the staging block; a thread then picks up its own row.
+                constexpr int CPG_IN = sizeof(OutT) == 2 ? 64 : 32;          // columns of a staged group (one 128-byte output row)
+                const int cg_in = (c0 - col_lo) % CPG_IN;
+                const int t128 = (q << 5) | lane;                            // thread index inside the half
+                auto stage_block = [&](const unsigned char *base, long long bs_bytes, long long rs_bytes, int esz, int first_col) {
+                    // [128 rows][128 bytes] of a tensor shaped like the output, starting at this CTA's first row and `first_col`
+                    const int row0 = mt * MT + (int)rank * kBM;
+                    const int per_piece = 16 / esz;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            if (col + i < a.N) {
-                                const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(gp + i));
-                                const __nv_bfloat16 *ge = reinterpret_cast<const __nv_bfloat16 *>(&raw);
+                    for (int it = 0; it < 8; ++it) {
+                        const int idx = it * 128 + t128, rr = idx >> 3, pc = idx & 7;
+                        uint4 val = make_uint4(0, 0, 0, 0);
+                        if (row0 + rr < a.rows && first_col + pc * per_piece < a.N)
+                            val = __ldg(reinterpret_cast<const uint4 *>(base + b * bs_bytes + (long long)(row0 + rr) * rs_bytes +
+                                                                         (long long)first_col * esz + pc * 16));
+                        *reinterpret_cast<uint4 *>(stg + rr * 128 + ((pc ^ (rr & 7)) << 4)) = val;
+                    }
+                    asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
+                };
+                auto staged_done = [&]() { asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory"); };
+                if (a.tma_store && e.gate != nullptr && sizeof(OutT) == 2) {
+                    // one staged group of the gate (64 bfloat16 per row) serves two 32-column chunks
+                    if (cg_in == 0) stage_block((const unsigned char *)e.gate, e.gate_bs * 2, e.gate_rs * 2, 2, col);
+                    const unsigned char *srow = stg + row_local * 128;
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) v[i + j] = (__bfloat162float(ge[j]) > 0.f) ? v[i + j] * e.gate_scale : 0.f;
-                            }
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 raw = *reinterpret_cast<const uint4 *>(srow + (((cg_in / 8 + i) ^ (row_local & 7)) << 4));
+                        const __nv_bfloat16 *ge = reinterpret_cast<const __nv_bfloat16 *>(&raw);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[8 * i + j] = (__bfloat162float(ge[j]) > 0.f) ? v[8 * i + j] * e.gate_scale : 0.f;
+                    }
+                    if (cg_in + 32 == CPG_IN) staged_done();
+                } else if (live && e.gate != nullptr) {
+                    // pass the value where the gate tensor (same shape as the output) is positive: the backward of
+                    // relu followed by dropout, whose forward output is the gate
+                    const __nv_bfloat16 *gp = (const __nv_bfloat16 *)e.gate + b * e.gate_bs + (int64_t)row * e.gate_rs + col;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        if (col + i < a.N) {
+                            const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(gp + i));
+                            const __nv_bfloat16 *ge = reinterpret_cast<const __nv_bfloat16 *>(&raw);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[i + j] = (__bfloat162float(ge[j]) > 0.f) ? v[i + j] * e.gate_scale : 0.f;
                         }
                     }
-                    if (e.residual != nullptr) {
-                        const float *rp = e.residual + b * e.res_bs + (int64_t)row * e.res_rs + col;
+                }
+                if (a.tma_store && e.residual != nullptr && sizeof(OutT) == 4) {
+                    stage_block((const unsigned char *)e.residual, e.res_bs * 4, e.res_rs * 4, 4, col);
+                    const unsigned char *srow = stg + row_local * 128;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            if (col + i < a.N) {
-                                const float4 rv = __ldg(reinterpret_cast<const float4 *>(rp + i));
-                                v[i] += rv.x; v[i + 1] += rv.y; v[i + 2] += rv.z; v[i + 3] += rv.w;
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 rv = *reinterpret_cast<const float4 *>(srow + ((i ^ (row_local & 7)) << 4));
+                        v[4 * i] += rv.x; v[4 * i + 1] += rv.y; v[4 * i + 2] += rv.z; v[4 * i + 3] += rv.w;
+                    }
+                    staged_done();
+                } else if (live && e.residual != nullptr) {
+                    const float *rp = e.residual + b * e.res_bs + (int64_t)row * e.res_rs + col;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        if (col + i < a.N) {
+                            const float4 rv = __ldg(reinterpret_cast<const float4 *>(rp + i));
+                            v[i] += rv.x; v[i + 1] += rv.y; v[i + 2] += rv.z; v[i + 3] += rv.w;
+                        }
+                    }
+                }
+                if (e.ce_partial != nullptr && live) {
+                    // logits as they are stored (rounded to bfloat16), classes [0, ce_classes): running max / sum of
+                    // exponentials, plain sum (label smoothing) and the target's logit
+                    float cm = ce_m;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+                        if (col + i < e.ce_classes) cm = fmaxf(cm, v[i]);
+                    }
+                    if (cm > -INFINITY) {
+                        float add = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (col + i < e.ce_classes) {
+                                add += __expf(v[i] - cm);
+                                ce_sx += v[i];
+                                if ((long long)(col + i) == ce_target) ce_xt = v[i];
                             }
                         }
+                        ce_s = ce_s * __expf(ce_m - cm) + add;
+                        ce_m = cm;
                     }
                 }
                 OutT *dst = (OutT *)a.c + b * a.c_bs + (int64_t)row * a.c_rs + col;
@@ -302,7 +371,9 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                         }
                     }
                 };
-                if (a.tma_store) {
+                if (e.ce_partial != nullptr && e.ce_skip_store) {
+                    // loss only: the logits are never written
+                } else if (a.tma_store) {
                     // Rows leave through the copy engine: the 4 warps of this half park a [128 rows][128 B] block in shared
                     // memory (swizzled like the tensor map expects) and one thread stores it with a single bulk copy, which
                     // writes whole lines and clips what lies outside the tensor.  Per-thread 16-byte stores would touch half
@@ -360,6 +431,9 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                     }
                 }
             }
+            if (a.epi.ce_partial != nullptr && row_ok)
+                *reinterpret_cast<float4 *>(a.epi.ce_partial + (((long long)b * a.rows + row) * (2 * a.n_tiles) + 2 * nt + half) * 4) =
+                    make_float4(ce_m, ce_s, ce_sx, ce_xt);
             fence_before_sync();
             __syncwarp();
             if (lane == 0) {                                  // the MMA thread (even CTA of a pair) may reuse the accumulator
@@ -467,6 +541,53 @@ static int sm_count() {
 
 using namespace hsa;
 
+namespace hsa {
+// Merge the per-tile-half statistics of a row into its loss and log-sum-exp (one thread per row).
+__global__ void __launch_bounds__(256)
+ce_combine_kernel(const float *__restrict__ partial, int slots, const long long *__restrict__ targets, float *__restrict__ loss_rows,
+                  float *__restrict__ lse_out, long long rows, int V, float eps, long long ignore_index) {
+    const long long r = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (r >= rows) return;
+    const float4 *p = reinterpret_cast<const float4 *>(partial) + r * slots;
+    float m = -INFINITY;
+    for (int i = 0; i < slots; ++i) m = fmaxf(m, p[i].x);
+    float s = 0.f, sx = 0.f, xt = 0.f;
+    for (int i = 0; i < slots; ++i) {
+        const float4 t = p[i];
+        if (t.x > -INFINITY) s += t.y * __expf(t.x - m);
+        sx += t.z;
+        xt += t.w;
+    }
+    const float lse = m + logf(s);
+    lse_out[r] = lse;
+    const long long tgt = targets[r];
+    float loss = 0.f;
+    if (tgt != ignore_index) {
+        if (tgt < 0 || tgt >= V) xt = __int_as_float(0x7fffffff);     // a corrupt label shows as NaN
+        loss = (1.f - eps) * (lse - xt) + eps * (lse - sx / (float)V);
+    }
+    loss_rows[r] = loss;
+}
+}  // namespace hsa
+
+extern "C" size_t hsa_linear_ce_partial_bytes(long long rows, int N) {
+    if (rows < 1 || N < 1) return 0;
+    const int BN = N > 128 ? 256 : 128;
+    return (size_t)rows * 2 * ((N + BN - 1) / BN) * 4 * sizeof(float);
+}
+
+extern "C" int hsa_linear_ce_combine(const float *partial, long long rows, int N, const long long *targets, float *loss_rows,
+                                     float *lse, int classes, float smoothing, long long ignore_index, void *stream) {
+    HSA_CHECK_ARG(partial && targets && loss_rows && lse, "hsa_linear_ce_combine: null pointer");
+    HSA_CHECK_ARG(rows >= 1 && N >= 1 && classes >= 1 && classes <= N, "hsa_linear_ce_combine: bad shape");
+    HSA_CHECK_ARG(smoothing >= 0.f && smoothing < 1.f, "hsa_linear_ce_combine: label smoothing %f outside [0, 1)", smoothing);
+    const int BN = N > 128 ? 256 : 128;
+    const int slots = 2 * ((N + BN - 1) / BN);
+    ce_combine_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, (cudaStream_t)stream>>>(partial, slots, targets, loss_rows, lse, rows,
+                                                                                      classes, smoothing, ignore_index);
+    return launch_status("hsa_linear_ce_combine");
+}
+
 extern "C" int hsa_gemm_aborts(unsigned int *count) {
     if (count == nullptr) return fail(HSA_ERR_ARG, "hsa_gemm_aborts: null pointer");
     cudaError_t e = cudaMemcpyFromSymbol(count, g_gemm_aborts, sizeof(unsigned int));
@@ -495,13 +616,23 @@ extern "C" size_t hsa_gemm_workspace_bytes(int batches, int rows, int N, int K, 
 extern "C" int hsa_gemm_choose_splits(int batches, int rows, int N, int K) {
     if (batches < 1 || rows < 1 || N < 1 || K < 1) return 1;
     const GemmShape sh = gemm_shape(rows, N);
-    const long long tiles = (long long)batches * ((rows + sh.MT - 1) / sh.MT) * ((N + sh.BN - 1) / sh.BN);
+    const long long m_tiles = (rows + sh.MT - 1) / sh.MT, n_tiles = (N + sh.BN - 1) / sh.BN;
+    const long long tiles = (long long)batches * m_tiles * n_tiles;
     const int k_blocks = (K + kBK - 1) / kBK;
     const int units = sh.two ? sm_count() / 2 : sm_count();        // tiles that run at once
-    if (tiles * 2 > units || k_blocks < 16) return 1;
-    long long s = units / tiles;
-    if (s > k_blocks / 4) s = k_blocks / 4;
-    return (int)(s < 1 ? 1 : s);
+    // Estimated time of s splits: waves of tiles, each (k_blocks / s) steps of ~0.38 us, plus writing and reading the
+    // float32 partial slabs.  Splitting pays when there are too few tiles to fill the GPU, or when the last wave of
+    // tiles would leave most of it idle and K is long enough to absorb the extra pass.
+    const double step_us = 0.38, bytes_per_us = 5.0e6;
+    double best = 1e30;
+    int best_s = 1;
+    for (int s = 1; s <= 32 && k_blocks / s >= 4; ++s) {
+        const long long waves = (tiles * s + units - 1) / units;
+        double t = (double)waves * ((k_blocks + s - 1) / s) * step_us;
+        if (s > 1) t += 2.0 * s * batches * m_tiles * sh.MT * n_tiles * sh.BN * 4.0 / bytes_per_us + 3.0;
+        if (t < best * 0.97) { best = t; best_s = s; }             // a later s must win by 3 %
+    }
+    return best_s;
 }
 
 // Layout codes: 0 = the operand is stored [rows, K] (K contiguous); 1 = stored transposed, [K, rows].
@@ -547,6 +678,9 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
                       "hsa_gemm_ex: gate must be 16-byte aligned");
         HSA_CHECK_ARG(e.copy_bf16 == nullptr || (out_dtype == HSA_F32 && aligned16(e.copy_bf16) && e.copy_rs % 8 == 0 && e.copy_bs % 8 == 0),
                       "hsa_gemm_ex: the bfloat16 copy needs a float32 main output and 16-byte alignment");
+        HSA_CHECK_ARG(e.ce_partial == nullptr || (e.ce_targets != nullptr && e.ce_classes >= 1 && e.ce_classes <= N && aligned16(e.ce_partial) &&
+                                                   out_dtype == HSA_BF16),
+                      "hsa_gemm_ex: bad cross-entropy description (bfloat16 logits, targets, 1 <= classes <= N)");
         HSA_CHECK_ARG(e.rng_state == nullptr || (e.drop_col_begin >= 0 && e.drop_col_end <= N && e.drop_site0 != 0 && e.drop_rows_total >= rows),
                       "hsa_gemm_ex: bad dropout description");
     }
@@ -594,7 +728,7 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
     // the output's tensor map (rows leave by bulk copies), unless the epilogue has to read C back or writes partial slabs
     CUtensorMap mc = ma;
     g.tma_store = 0;
-    if (g.partial == nullptr && !accumulate && make_map_out(&mc, C.ptr, N, rows, out_batches, C.row_stride, C.batch_stride, esz))
+    if (g.partial == nullptr && !accumulate && !(epilogue && epilogue->ce_partial && epilogue->ce_skip_store) && make_map_out(&mc, C.ptr, N, rows, out_batches, C.row_stride, C.batch_stride, esz))
         g.tma_store = 1;
     const long long total = (long long)g.m_tiles * g.n_tiles * g.batches * g.splits;
     if (total > 0x7fffffffLL) return fail(HSA_ERR_ARG, "hsa_gemm: too many tiles");

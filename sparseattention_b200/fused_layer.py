@@ -113,6 +113,65 @@ def _span_bwd(q, k, v, out, lse, dout, dq, dk, dv, N, H, R, causal):
     _lib.check(rc, "hsa_span_attn_bwd")
 
 
+# Levels from this one up run as one cooperative launch per tree and direction (csrc/parent_tree.cu); the levels below
+# it are large enough for a launch per level to stream at HBM speed.  None switches the tree kernel off.
+TREE_START_LEVEL: Optional[int] = 2
+
+
+def _tree_start(L: int, d: int) -> Optional[int]:
+    if TREE_START_LEVEL is None or d % 256 != 0:
+        return None
+    start = max(1, int(TREE_START_LEVEL))
+    return start if start < L else None
+
+
+def _tree_state(dev) -> torch.Tensor:
+    return torch.empty(int(_lib.load().hsa_parent_tree_state_bytes()) // 4, dtype=torch.int32, device=dev)
+
+
+def _tree_drop(spec):
+    if spec is None:
+        return None, 0, 0, 1.0
+    return c_void_p(spec.key.data_ptr()), spec.site0, spec.threshold, spec.scale
+
+
+def _parent_tree_fwd(QKVp, Rb, KVc, Wkv, N, H, start, spec):
+    lib = _lib.load()
+    B, M, d3 = QKVp.shape
+    d = d3 // 3
+    state = _tree_state(QKVp.device)
+    key, site, thr, scale = _tree_drop(spec)
+    rc = lib.hsa_parent_tree_fwd(_lib.rows_view(QKVp[..., :d]), _lib.rows_view(QKVp[..., d:2 * d]), _lib.rows_view(QKVp[..., 2 * d:]),
+                                 _lib.rows_view(Rb), _lib.rows_view(KVc), _ptr(Wkv), B, N, H, d // H, start, key, site, thr, scale,
+                                 _ptr(state), _lib.stream_ptr(QKVp.device))
+    _lib.check(rc, "hsa_parent_tree_fwd")
+    return state
+
+
+def _parent_tree_bwd(QKVp, KVc, dRf, dRb, dQKVp, dKVc, Wkv, N, H, start, spec):
+    lib = _lib.load()
+    B, M, d3 = QKVp.shape
+    d = d3 // 3
+    state = _tree_state(QKVp.device)
+    key, site, thr, scale = _tree_drop(spec)
+    rc = lib.hsa_parent_tree_bwd(_lib.rows_view(QKVp[..., :d]), _lib.rows_view(QKVp[..., d:2 * d]), _lib.rows_view(QKVp[..., 2 * d:]),
+                                 _lib.rows_view(KVc), _lib.rows_view(dRf), _lib.rows_view(dRb), _lib.rows_view(dQKVp[..., :d]),
+                                 _lib.rows_view(dQKVp[..., d:2 * d]), _lib.rows_view(dQKVp[..., 2 * d:]), _lib.rows_view(dKVc),
+                                 _ptr(Wkv), B, N, H, d // H, start, key, site, thr, scale, _ptr(state),
+                                 _lib.stream_ptr(QKVp.device))
+    _lib.check(rc, "hsa_parent_tree_bwd")
+    return state
+
+
+def parent_tree_status(state: torch.Tensor) -> int:
+    """0 when every level of the tree launch that used `state` completed; non-zero when a thread block gave up at the
+    grid barrier (1) or inside a level (2).  Synchronises."""
+    import ctypes
+    st = ctypes.c_uint(0)
+    _lib.check(_lib.load().hsa_parent_tree_status(_ptr(state), ctypes.byref(st)), "hsa_parent_tree_status")
+    return int(st.value)
+
+
 def level_layout(N: int) -> Tuple[List[int], List[int]]:
     sizes, offsets, off = [], [], 0
     n = N
@@ -157,7 +216,12 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
             KVc0 = gemm(xb, Wkv_y, dropout=drop(S_LEAF_A, S_LEAF_B), drop_cols=(d, 2 * d))       # leaf values dropped twice
             Rb = new(B, M, d)                                                   # refreshed parents, level after level
             KVc = new(B, M, 2 * d)                                              # child projections of levels >= 1 (row = child's row in Rb)
+            tree_start = _tree_start(len(sizes), d)
             for lvl, (P, off) in enumerate(zip(sizes, offs)):
+                if tree_start is not None and lvl >= tree_start:
+                    # every level from here up in one cooperative launch
+                    _parent_tree_fwd(QKVp, Rb, KVc, Wkv_y, N, H, tree_start, drop(S_CHILD))
+                    break
                 if lvl == 0:
                     kc, vc = KVc0[..., :d], KVc0[..., d:]
                 else:
@@ -258,7 +322,12 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
             dQKVp = new(B, M, 3 * d)
             dKVc = new(B, M, 2 * d)
             dKVc0 = new(B, N, 2 * d)
-            for lvl in range(len(sizes) - 1, -1, -1):
+            tree_start = _tree_start(len(sizes), d)
+            top = len(sizes) - 1
+            if tree_start is not None:
+                _parent_tree_bwd(QKVp, KVc, dRf, dRb, dQKVp, dKVc, Wkv_y, N, H, tree_start, spec(S_CHILD))
+                top = tree_start - 1
+            for lvl in range(top, -1, -1):
                 P, off = sizes[lvl], offs[lvl]
                 sl, dsl = QKVp[:, off:off + P], dQKVp[:, off:off + P]
                 if lvl == 0:

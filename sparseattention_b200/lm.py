@@ -29,7 +29,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .modules.attention import HierarchicalAttention
-from .ops.loss import cross_entropy
+from .ops.loss import cross_entropy, linear_cross_entropy
 from .ops.norm import LayerNorm
 from .ops.topology import generate_span_input_Y
 
@@ -122,9 +122,10 @@ class TransformerLM(nn.Module):
         elif isinstance(module, nn.Embedding):
             torch.nn.init.normal_(module.weight, mean=0.0, std=0.02)
 
-    def forward(self, trg, return_attention: bool = False, padded_logits: bool = False):
+    def forward(self, trg, return_attention: bool = False, padded_logits: bool = False, hidden_only: bool = False):
         """Logits [B, N, vocab_size]; with padded_logits=True the [B, N, vocab_padded] tensor the LM head
-        produces (columns >= vocab_size are padding), which `lm_loss` consumes without a copy."""
+        produces (columns >= vocab_size are padding), which `lm_loss` consumes without a copy; with
+        hidden_only=True the last hidden states [B, N, d_model] (the LM head is then applied by the caller)."""
         x = self.embedding(trg) * math.sqrt(self.d_model)
         x = self.pos_encoding(x)
         y = self._span_init(x)
@@ -134,6 +135,8 @@ class TransformerLM(nn.Module):
                 x, y, _ = layer(x, y, mask=causal_flag, return_attention=True)
             else:
                 x, y = layer(x, y, mask=causal_flag)
+        if hidden_only:
+            return x
         logits = self.fc_out(x)
         return logits if padded_logits else logits[..., : self.vocab_size]
 
@@ -271,6 +274,13 @@ def lm_loss(model: "TransformerLM", tokens: torch.Tensor, label_smoothing: float
     """Next-token cross entropy on a [B, N+1] window: input = window[:, :-1], labels = window[:, 1:]
     (the reference's loader and criterion, Pretrain.py:181-194, 514), computed by the library's
     cross-entropy kernel straight on the padded logits."""
+    if (tokens.is_cuda and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16
+            and model.d_model % 8 == 0):
+        # bf16 autocast: LM head and loss in one pass (tcgen05 product whose epilogue keeps the softmax statistics)
+        hidden = model(tokens[:, :-1], hidden_only=True)
+        return linear_cross_entropy(hidden.reshape(-1, hidden.size(-1)), model.fc_out.weight, model.fc_out.bias,
+                                    tokens[:, 1:].reshape(-1), model.vocab_size, label_smoothing=label_smoothing,
+                                    ignore_index=ignore_index)
     logits = model(tokens[:, :-1], padded_logits=True)
     return cross_entropy(logits.reshape(-1, logits.size(-1)), tokens[:, 1:].reshape(-1), model.vocab_size,
                          label_smoothing=label_smoothing, ignore_index=ignore_index)

@@ -61,7 +61,8 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
          splits: Optional[int] = None, relu: bool = False, dropout: Optional[DropoutSpec] = None,
          drop_cols: Optional[tuple] = None, drop_rows_total: Optional[int] = None, drop_row_offset: int = 0,
          gate: Optional[torch.Tensor] = None, gate_scale: float = 1.0, residual: Optional[torch.Tensor] = None,
-         copy_bf16: Optional[torch.Tensor] = None) -> torch.Tensor:
+         copy_bf16: Optional[torch.Tensor] = None, ce_partial: Optional[torch.Tensor] = None,
+         ce_targets: Optional[torch.Tensor] = None, ce_classes: int = 0, ce_skip_store: bool = False) -> torch.Tensor:
     """C = A @ op(B) (+ bias), bfloat16 operands, float32 accumulation.  No autograd.
 
     a_t=False: A [batches, rows, K] (or [rows, K]); B is one matrix: [N, K] (b_t=False, C = A B^T) or [K, N] (b_t=True,
@@ -73,7 +74,9 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     Fused tail (see hsa_gemm_epilogue): relu; `dropout` on columns drop_cols=(begin, end) (default: all), element ids
     relative to a logical tensor of drop_rows_total rows per batch entry of which this product writes rows
     drop_row_offset..; `gate` (bfloat16, shaped like the output): v = gate > 0 ? v * gate_scale : 0; `residual`
-    (float32, shaped like the output) added last; `copy_bf16`: a bfloat16 copy of a float32 output.
+    (float32, shaped like the output) added last; `copy_bf16`: a bfloat16 copy of a float32 output;
+    `ce_partial` / `ce_targets` / `ce_classes`: cross-entropy statistics of the output taken as logits (see
+    ops.loss.linear_cross_entropy), with ce_skip_store the logits themselves are not written.
     """
     lib = _lib.load()
     dev = _lib.require_cuda(A, B)
@@ -96,6 +99,9 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         out_shape = (rows, N) if squeeze else (batches, rows, N)
     odt = out_dtype or (out.dtype if out is not None else torch.bfloat16)
     assert odt in (torch.bfloat16, torch.float32)
+    if out is None and ce_skip_store:
+        out = torch.empty(out_shape[:-1] + (8,), dtype=odt, device=dev)           # never written: only its pointer is passed
+        out_shape = tuple(out.shape)
     if out is None:
         assert not accumulate, "accumulate needs an `out` tensor"
         out = torch.empty(out_shape, dtype=odt, device=dev)
@@ -110,7 +116,7 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         assert bias32.numel() == N
     ob = 1 if a_t else batches
     epi = None
-    if relu or dropout is not None or gate is not None or residual is not None or copy_bf16 is not None:
+    if relu or dropout is not None or gate is not None or residual is not None or copy_bf16 is not None or ce_partial is not None:
         assert not a_t, "a fused tail needs the plain A layout"
         epi = _lib.GemmEpilogue()
         epi.relu = int(relu)
@@ -136,6 +142,11 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
             else:
                 epi.copy_bf16, epi.copy_bs, epi.copy_rs = t3.data_ptr(), t3.stride(0), t3.stride(1)
             keep.append(t3)
+        if ce_partial is not None:
+            assert ce_targets is not None and ce_targets.dtype == torch.int64 and ce_targets.numel() == batches * rows
+            assert ce_partial.dtype == torch.float32 and ce_partial.is_contiguous() and ce_targets.is_contiguous()
+            epi.ce_partial, epi.ce_targets = ce_partial.data_ptr(), ce_targets.data_ptr()
+            epi.ce_classes, epi.ce_skip_store = int(ce_classes), int(ce_skip_store)
         splits = 1
     if splits is None:
         splits = int(lib.hsa_gemm_choose_splits(ob, rows, N, K * (batches if a_t else 1)))

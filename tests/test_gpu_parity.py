@@ -525,6 +525,69 @@ def test_fused_decoder_layer_against_eager(hsa, shape):
         assert rel_err(fused[name], want[name]) < bound, name
 
 
+@pytest.mark.parametrize("shape", [(2, 256, 256, 4, 512), (1, 2048, 512, 8, 512), (2, 512, 512, 4, 256)])
+@pytest.mark.parametrize("p", [0.0, 0.1])
+def test_parent_tree_launch_matches_per_level(hsa, shape, p):
+    """One cooperative launch per tree (from level 1, and from level 3) against the launch-per-level path of the fused
+    layer, same dropout key: outputs and all gradients agree to bfloat16 accuracy (the two paths round a few values
+    differently in the last bit, which the relu gate of the feed-forward can amplify to a few percent in single entries
+    of fc1's gradient; hence 5e-2 on the maximum and 1e-2 on the mean measure)."""
+    import sparseattention_b200.fused_layer as fl
+    from sparseattention_b200.lm import DecoderLayer
+    B, N, d, H, ff = shape
+    torch.manual_seed(N)
+    layer = DecoderLayer(d, H, ff, dropout=p, window_size=16).cuda().train()
+    x = torch.randn(B, N, d, device="cuda")
+    y = torch.randn(B, N - 1, d, device="cuda")
+    gx, gy = torch.randn_like(x), torch.randn_like(y)
+    cfg = {"heads": H, "window": 16, "causal": True, "p": p, "eps": 1e-5}
+    key = torch.tensor([4242], dtype=torch.int64, device="cuda")
+    prm = list(fl.fused_layer_parameters(layer))
+    results = {}
+    old = fl.TREE_START_LEVEL
+    try:
+        for start in (None, 1, 3):
+            fl.TREE_START_LEVEL = start
+            for q in prm:
+                q.grad = None
+            xg, yg = x.clone().requires_grad_(), y.clone().requires_grad_()
+            xo, yo = fl.FusedDecoderLayerFunction.apply(xg, yg, cfg, key, *prm)
+            ((xo * gx).sum() + (yo * gy).sum()).backward()
+            results[start] = [xo.detach(), yo.detach(), xg.grad, yg.grad] + [q.grad.clone() for q in prm]
+    finally:
+        fl.TREE_START_LEVEL = old
+    from tests.conftest import max_rel_err, mean_rel_err
+    for start in (1, 3):
+        for got, want in zip(results[start], results[None]):
+            assert max_rel_err(got.float().cpu(), want.float().cpu()) < 5e-2, start
+            assert mean_rel_err(got.float().cpu(), want.float().cpu()) < 1e-2, start
+
+
+def test_parent_tree_bounded_barrier(hsa):
+    """The grid barrier of the tree launch gives up instead of hanging: with the test hook the barrier waits for one
+    arrival more than there are thread blocks and for about a millisecond only; every block must leave, the status word
+    must say so, and the next launch (hook off) must complete normally."""
+    import sparseattention_b200.fused_layer as fl
+    from sparseattention_b200 import _lib
+    lib = _lib.load()
+    B, N, d, H = 1, 256, 256, 4
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    QKVp = torch.randn(B, N - 1, 3 * d, generator=gen, device="cuda").bfloat16()
+    Rb = torch.randn(B, N - 1, d, generator=gen, device="cuda").bfloat16()
+    KVc = torch.zeros(B, N - 1, 2 * d, device="cuda", dtype=torch.bfloat16)
+    W = (torch.randn(2 * d, d, generator=gen, device="cuda") * 0.05).bfloat16()
+    try:
+        _lib.check(lib.hsa_debug_wait_test(2_000_000, 1), "hsa_debug_wait_test")
+        state = fl._parent_tree_fwd(QKVp, Rb.clone(), KVc, W, N, H, 1, None)
+        assert fl.parent_tree_status(state) == 1
+    finally:
+        _lib.check(lib.hsa_debug_wait_test(2_000_000_000, 0), "hsa_debug_wait_test")
+    R2 = Rb.clone()
+    state = fl._parent_tree_fwd(QKVp, R2, KVc, W, N, H, 1, None)
+    assert fl.parent_tree_status(state) == 0
+    assert bool(torch.isfinite(R2.float()).all()) and not torch.equal(R2[:, N // 2:], Rb[:, N // 2:])
+
+
 def test_fused_decoder_layer_dropout(hsa):
     """With dropout the fused layer draws a new mask per call, yet forward and backward of one call agree on it: the
     layer is linear in the feed-forward output bias, so the gradient of sum(x_out) for that bias must equal the
@@ -985,6 +1048,37 @@ def test_cross_entropy_vs_torch(hsa, M, V, Vp, dtype, eps):
     assert abs(float(out.detach()) - float(ref.detach())) <= 1e-5 * abs(float(ref.detach())) + 1e-6
     assert rel_err(x.grad[:, :V].float().cpu(), ref_in.grad) < tol
     assert float(x.grad[:, V:].abs().sum()) == 0.0 and float(x.grad[0].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("M,d,V,Vp", [(300, 64, 211, 256), (1000, 512, 50257, 50304), (129, 128, 1000, 1000)])
+@pytest.mark.parametrize("eps", [0.0, 0.1])
+def test_linear_cross_entropy_vs_torch(hsa, M, d, V, Vp, eps):
+    """LM head + loss in one pass against float64 F.linear + F.cross_entropy on the same bf16-rounded operands:
+    loss, and the gradients of x, weight and bias; the loss-only path (no logits written) gives the same value."""
+    from sparseattention_b200.ops.loss import linear_cross_entropy
+    gen = torch.Generator().manual_seed(M + V)
+    x = torch.randn(M, d, generator=gen).bfloat16()
+    w = (torch.randn(Vp, d, generator=gen) * 0.05).bfloat16()
+    b = torch.randn(Vp, generator=gen) * 0.1
+    targets = torch.randint(0, V, (M,), generator=gen)
+    targets[3] = -100
+    xr, wr, br = x.double().requires_grad_(), w.double().requires_grad_(), b.double().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(torch.nn.functional.linear(xr, wr, br)[:, :V], targets, label_smoothing=eps, ignore_index=-100)
+    ref.backward()
+    xc, wc, bc = x.cuda().requires_grad_(), w.cuda().requires_grad_(), b.cuda().requires_grad_()
+    out = linear_cross_entropy(xc, wc, bc, targets.cuda(), V, label_smoothing=eps, ignore_index=-100)
+    out.backward()
+    assert abs(float(out.detach()) - float(ref.detach())) < 2e-3 * abs(float(ref.detach()))     # logits rounded to bf16
+    assert rel_err(xc.grad.float().cpu(), xr.grad) < 2e-2
+    assert rel_err(wc.grad.float().cpu()[:V], wr.grad[:V]) < 2e-2 and float(wc.grad[V:].abs().max() if Vp > V else 0) == 0.0
+    assert rel_err(bc.grad.cpu()[:V], br.grad[:V]) < 2e-2
+    with torch.no_grad():
+        loss_only = linear_cross_entropy(x.cuda(), w.cuda(), b.cuda(), targets.cuda(), V, label_smoothing=eps, ignore_index=-100)
+    assert abs(float(loss_only) - float(out.detach())) < 1e-6 * abs(float(out.detach()))
+    bad = targets.clone()
+    bad[5] = V + 3
+    with torch.no_grad():
+        assert bool(linear_cross_entropy(x.cuda(), w.cuda(), b.cuda(), bad.cuda(), V).isnan())
 
 
 def test_host_entry_point_matches_device_path(hsa):
