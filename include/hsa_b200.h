@@ -367,6 +367,23 @@ int hsa_dropout_apply(hsa_view in, int in_dtype, hsa_view out, int batches, int 
                       unsigned int threshold, float scale, void *stream);
 
 /*
+ * Column sums of a bfloat16 matrix, out[c] = sum_r x[r, c] in float32, in a fixed order: the bias gradients of the
+ * projections (the reference leaves them to autograd's reduction kernels).  `partial` holds
+ * hsa_column_sums_partial_bytes(rows, cols) bytes.  cols and row_stride multiples of 8.
+ */
+size_t hsa_column_sums_partial_bytes(long long rows, int cols);
+int hsa_column_sums(const void *x, long long row_stride, long long rows, int cols, float *out, float *partial, void *stream);
+
+/*
+ * hsa_cross_entropy_bwd for bfloat16 logits IN PLACE (the logits are overwritten by their gradient) together with the
+ * column sums of that gradient, col_sums [Vp] float32: the bias gradient of the LM head, which otherwise costs another
+ * pass over the [tokens, vocabulary] matrix.  `partial`: hsa_column_sums_partial_bytes(rows, Vp) bytes.
+ */
+int hsa_cross_entropy_bwd_inplace(void *logits, long long row_stride, const long long *targets, const float *lse,
+                                  const float *grad_scale, long long rows, int V, int Vp, float smoothing,
+                                  long long ignore_index, float *col_sums, float *partial, void *stream);
+
+/*
  * Span attention backward without any workspace argument.  No counterpart in the reference
  * project: it exists for hosts that cannot allocate device memory around the call (a plugin
  * execute hook that only receives pre-bound buffers; a server whose GPU memory is fully

@@ -55,9 +55,161 @@ dropout_apply_kernel(DropArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------- column sums
+// out[c] = sum over rows of x[r, c] (bias gradients).  A thread owns 8 consecutive columns and every fourth row of a block
+// of kCsRows rows; the four row lanes are combined through shared memory, blocks by a second kernel in block order.
+constexpr int kCsRows = 256;
+
+// `rows4(r, n, col, v)` yields the values of rows r, r+4, .. (n <= 4 of them) at columns col..col+7, having issued all
+// of their loads before anything depends on one (one load in flight per thread leaves HBM mostly idle).
+template <typename F>
+__device__ __forceinline__ void colsum_block(int rows_here, int cols, int col0, float *__restrict__ partial_row, F &&rows4) {
+    __shared__ float red[4][64][8];
+    const int cx = threadIdx.x & 63, ry = threadIdx.x >> 6;
+    const int col = col0 + 8 * cx;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (col < cols) {
+        for (int r = ry; r < rows_here; r += 16) {
+            float v[4][8];
+            const int n = min(4, (rows_here - r + 3) / 4);
+            rows4(r, n, col, v);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (u < n) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] += v[u][i];
+                }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[ry][cx][i] = acc[i];
+    __syncthreads();
+    if (ry == 0 && col < cols) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) partial_row[col + i] = (red[0][cx][i] + red[1][cx][i]) + (red[2][cx][i] + red[3][cx][i]);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+column_sums_kernel(const __nv_bfloat16 *__restrict__ x, int64_t row_stride, int64_t rows, int cols, float *__restrict__ partial) {
+    const int64_t r0 = (int64_t)blockIdx.y * kCsRows;
+    const int rows_here = (int)((rows - r0) < kCsRows ? (rows - r0) : kCsRows);
+    colsum_block(rows_here, cols, blockIdx.x * 512, partial + (int64_t)blockIdx.y * cols, [&](int r, int n, int col, float (&v)[4][8]) {
+        uint4 raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (u < n) raw[u] = __ldg(reinterpret_cast<const uint4 *>(x + (r0 + r + 4 * u) * row_stride + col));
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (u < n) {
+                const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&raw[u]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[u][i] = __bfloat162float(e[i]);
+            }
+    });
+}
+
+__global__ void __launch_bounds__(256)
+column_sums_reduce_kernel(const float *__restrict__ partial, int blocks, int cols, float *__restrict__ out) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (int b = 0; b < blocks; ++b) s += partial[(int64_t)b * cols + c];
+    out[c] = s;
+}
+
+// Backward of the label-smoothed cross entropy IN PLACE (the logits become their gradient) together with the column
+// sums of that gradient (the bias gradient of the layer that produced the logits): a block walks kCsRows rows of a slab
+// of 512 columns, so the sums come for free and the separate reduction pass over the [tokens, vocabulary] matrix goes away.
+__global__ void __launch_bounds__(256)
+ce_bwd_colsum_kernel(__nv_bfloat16 *logits, int64_t row_stride, const long long *__restrict__ targets, const float *__restrict__ lse,
+                     const float *__restrict__ grad_scale, int64_t rows, int V, int Vp, float eps, long long ignore_index,
+                     float *__restrict__ partial) {
+    const int64_t r0 = (int64_t)blockIdx.y * kCsRows;
+    const int rows_here = (int)((rows - r0) < kCsRows ? (rows - r0) : kCsRows);
+    const float g0 = grad_scale[0], sm = eps / (float)V;
+    colsum_block(rows_here, Vp, blockIdx.x * 512, partial + (int64_t)blockIdx.y * Vp, [&](int r, int n, int col, float (&v)[4][8]) {
+        uint4 raw[4];
+        long long tgt[4];
+        float l[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (u < n) {
+                const int64_t row = r0 + r + 4 * u;
+                raw[u] = *reinterpret_cast<const uint4 *>(logits + row * row_stride + col);
+                tgt[u] = targets[row];
+                l[u] = lse[row];
+            }
+        constexpr float kL2e = 1.4426950408889634f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (u < n) {
+                const uint32_t *w = reinterpret_cast<const uint32_t *>(&raw[u]);
+                const float g = tgt[u] == ignore_index ? 0.f : g0;
+                const float gs = g * sm, gt = g * (1.f - eps), l2 = l[u] * kL2e;
+                const long long tdiff = tgt[u] - col;
+                const int tcol = (tdiff >= 0 && tdiff < 8) ? (int)tdiff : -1;      // the target's column inside these 8, if any
+                const int nv = V - col;                                               // classes among these 8 columns
+                uint4 o;
+                uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    // two bfloat16 logits per word: the low half is element i, the high half element i+1
+                    const float x0 = __uint_as_float(w[i / 2] << 16), x1 = __uint_as_float(w[i / 2] & 0xffff0000u);
+                    float d0, d1;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(d0) : "f"(fmaf(x0, kL2e, -l2)));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(d1) : "f"(fmaf(x1, kL2e, -l2)));
+                    d0 = fmaf(d0, g, -gs) - (i == tcol ? gt : 0.f);
+                    d1 = fmaf(d1, g, -gs) - (i + 1 == tcol ? gt : 0.f);
+                    if (i >= nv) d0 = 0.f;
+                    if (i + 1 >= nv) d1 = 0.f;
+                    v[u][i] = d0;
+                    v[u][i + 1] = d1;
+                    const __nv_bfloat162 pk = __floats2bfloat162_rn(d0, d1);
+                    ow[i / 2] = *reinterpret_cast<const uint32_t *>(&pk);
+                }
+                *reinterpret_cast<uint4 *>(logits + (r0 + r + 4 * u) * row_stride + col) = o;
+            }
+    });
+}
+
 }  // namespace hsa
 
 using namespace hsa;
+
+extern "C" size_t hsa_column_sums_partial_bytes(long long rows, int cols) {
+    if (rows < 1 || cols < 1) return 0;
+    return (size_t)((rows + kCsRows - 1) / kCsRows) * cols * sizeof(float);
+}
+
+extern "C" int hsa_column_sums(const void *x, long long row_stride, long long rows, int cols, float *out, float *partial, void *stream) {
+    HSA_CHECK_ARG(x && out && partial, "hsa_column_sums: null pointer");
+    HSA_CHECK_ARG(rows >= 1 && cols >= 8 && cols % 8 == 0 && row_stride % 8 == 0 && aligned16(x), "hsa_column_sums: bad shape or alignment");
+    const int blocks = (int)((rows + kCsRows - 1) / kCsRows);
+    HSA_CHECK_ARG(blocks <= 65535, "hsa_column_sums: too many rows");
+    dim3 grid((unsigned)((cols + 511) / 512), (unsigned)blocks);
+    column_sums_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)x, row_stride, rows, cols, partial);
+    if (int rc = launch_status("hsa_column_sums")) return rc;
+    column_sums_reduce_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, (cudaStream_t)stream>>>(partial, blocks, cols, out);
+    return launch_status("hsa_column_sums(reduce)");
+}
+
+extern "C" int hsa_cross_entropy_bwd_inplace(void *logits, long long row_stride, const long long *targets, const float *lse,
+                                             const float *grad_scale, long long rows, int V, int Vp, float smoothing,
+                                             long long ignore_index, float *col_sums, float *partial, void *stream) {
+    HSA_CHECK_ARG(logits && targets && lse && grad_scale && col_sums && partial, "hsa_cross_entropy_bwd_inplace: null pointer");
+    HSA_CHECK_ARG(rows >= 1 && V >= 1 && Vp >= V && Vp % 8 == 0 && row_stride >= Vp && row_stride % 8 == 0 && aligned16(logits),
+                  "hsa_cross_entropy_bwd_inplace: bad shape or alignment");
+    HSA_CHECK_ARG(smoothing >= 0.f && smoothing < 1.f, "hsa_cross_entropy_bwd_inplace: label smoothing %f outside [0, 1)", smoothing);
+    const int blocks = (int)((rows + kCsRows - 1) / kCsRows);
+    HSA_CHECK_ARG(blocks <= 65535, "hsa_cross_entropy_bwd_inplace: too many rows");
+    dim3 grid((unsigned)((Vp + 511) / 512), (unsigned)blocks);
+    ce_bwd_colsum_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16 *)logits, row_stride, targets, lse, grad_scale, rows, V,
+                                                                Vp, smoothing, ignore_index, partial);
+    if (int rc = launch_status("hsa_cross_entropy_bwd_inplace")) return rc;
+    column_sums_reduce_kernel<<<(unsigned)((Vp + 255) / 256), 256, 0, (cudaStream_t)stream>>>(partial, blocks, Vp, col_sums);
+    return launch_status("hsa_cross_entropy_bwd_inplace(reduce)");
+}
 
 extern "C" int hsa_dropout_apply(hsa_view in, int in_dtype, hsa_view out, int batches, int rows, int col_begin, int ncols,
                                  long long N, long long rows_total, long long row_offset, long long col_shift,

@@ -21,6 +21,7 @@
 // float32 partial tiles are summed in a fixed order by a second kernel.
 // Every mbarrier wait is bounded; a CTA whose wait runs out raises a flag the other roles see, counts itself in
 // g_gemm_aborts (hsa_gemm_aborts reads it), frees its tensor memory and returns.
+#include <cstdlib>
 #include <mutex>
 
 #include "hsa_common.cuh"
@@ -51,6 +52,12 @@ struct GemmArgs {
 
 __device__ unsigned int g_gemm_aborts = 0;
 
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // TWO: the tile is 256 x BN and belongs to a pair of CTAs (cluster of two, tcgen05 cta_group::2): each CTA stages its
 // own 128 rows of A and half of the B tile, so a stage is 32 KB instead of 48 KB per 128 output rows and every byte
 // fetched from L2 feeds twice the arithmetic.  With this model's short reductions (K = 512) the single-CTA form is
@@ -72,7 +79,8 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     unsigned char *staging = smem + (size_t)STAGES * STAGE;           // 2 x 16 KB: one block of output rows per column half
-    unsigned long long *bars = reinterpret_cast<unsigned long long *>(staging + 32768);
+    float *bias_s = reinterpret_cast<float *>(staging + 32768);        // the tile's bias values, 128 per column half
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(staging + 32768 + 1024);
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -100,6 +108,11 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
     __syncthreads();
     if constexpr (TWO) cluster_sync();                 // the partner's barriers exist before anything signals them
     fence_after_sync();
+    // Programmatic dependent launch: everything above (barriers, tensor memory, descriptor prefetch) may overlap the tail
+    // of the previous kernel in the stream; nothing below runs before that kernel has completed and its writes are visible.
+    // The next kernel launched this way may in turn begin its own set-up while this one is still working.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
     const int tiles_mn = a.m_tiles * a.n_tiles * a.batches;
@@ -196,9 +209,38 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
         const int col_lo = ((warp - 2) >> 2) * (BN / 2);   // ... and the half of the tile's columns it owns
         int acc = 0; uint32_t acc_ph = 0;
         bool ok = true;
+        const unsigned long long drop_key = a.epi.rng_state != nullptr ? *a.epi.rng_state : 0ull;
+        // Gate / residual blocks ([128 rows][128 bytes] of a tensor shaped like the output) are fetched one block AHEAD into
+        // registers, 8 threads per row (whole lines), so their latency hides behind the previous block's work; the first
+        // block of a tile is requested before the accumulator is even waited for.
+        const bool in_gate = a.tma_store && a.epi.gate != nullptr && sizeof(OutT) == 2;
+        const bool in_res = a.tma_store && a.epi.residual != nullptr && sizeof(OutT) == 4;
+        const int t128 = ((warp & 3) << 5) | lane;                           // thread index inside the column half
+        uint4 pre[8];
+        auto fetch_block = [&](int bb, int row0, int first_col) {
+            const unsigned char *base = in_gate ? (const unsigned char *)a.epi.gate : (const unsigned char *)a.epi.residual;
+            const long long bs = in_gate ? a.epi.gate_bs * 2 : a.epi.res_bs * 4, rs = in_gate ? a.epi.gate_rs * 2 : a.epi.res_rs * 4;
+            const int esz = in_gate ? 2 : 4, per_piece = 16 / esz;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int idx = it * 128 + t128, rr = idx >> 3, pc = idx & 7;
+                pre[it] = make_uint4(0, 0, 0, 0);
+                if (row0 + rr < a.rows && first_col + pc * per_piece < a.N)
+                    pre[it] = __ldg(reinterpret_cast<const uint4 *>(base + bb * bs + (long long)(row0 + rr) * rs +
+                                                                    (long long)first_col * esz + pc * 16));
+            }
+        };
         for (int t = unit; t < total && ok; t += nunits) {
             int sp, b, mt, nt;
             decode(t, sp, b, mt, nt);
+            if (in_gate || in_res) fetch_block(b, mt * MT + (int)rank * kBM, nt * BN + ((warp - 2) >> 2) * (BN / 2));
+            if (a.bias != nullptr && a.partial == nullptr) {
+                // this half's 128 bias values, fetched before the accumulator is waited for (a global load inside the
+                // column loop would sit on the critical path of every chunk)
+                const int hb = (warp - 2) >> 2, j = ((warp & 3) << 5) | lane;
+                const int cidx = nt * BN + hb * (BN / 2) + j;
+                if (j < BN / 2) bias_s[hb * 128 + j] = cidx < a.N ? __ldg(a.bias + cidx) : 0.f;
+            }
             ok = mbar_wait(acc_full(acc), acc_ph, a.wait_limit, abort_flag);
             {   // the four warps that share a staging block go on (or give up) together
                 uint32_t all_ok;
@@ -240,13 +282,12 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                 for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
                 const hsa_gemm_epilogue &e = a.epi;
                 if (live) {
-                    if (a.bias != nullptr) {
+                    if (a.bias != nullptr) {                 // visible since the barrier that follows the accumulator wait
+                        const float *bs = bias_s + half * 128 + (c0 - col_lo);
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
-                            if (col + i < a.N) {
-                                const float4 bv = __ldg(reinterpret_cast<const float4 *>(a.bias + col + i));
-                                v[i] += bv.x; v[i + 1] += bv.y; v[i + 2] += bv.z; v[i + 3] += bv.w;
-                            }
+                            const float4 bv = *reinterpret_cast<const float4 *>(bs + i);
+                            v[i] += bv.x; v[i + 1] += bv.y; v[i + 2] += bv.z; v[i + 3] += bv.w;
                         }
                     }
                     if (e.relu) {
@@ -256,7 +297,7 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                     if (e.rng_state != nullptr && col + 32 > e.drop_col_begin && col < e.drop_col_end) {
                         // dropout on columns [drop_col_begin, drop_col_end): element id = (batch, row, column) of the logical
                         // [batches, drop_rows_total, N] tensor this product writes a row range of
-                        const unsigned long long key = *e.rng_state;
+                        const unsigned long long key = drop_key;
                         const unsigned long long id0 = ((unsigned long long)b * e.drop_rows_total + (unsigned long long)(row + e.drop_row_offset)) *
                                                        (unsigned long long)a.N + (unsigned long long)col;
 #pragma unroll
@@ -273,26 +314,21 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                 // (whole lines, like the output block leaves), through the staging block; a thread then picks up its own row.
                 constexpr int CPG_IN = sizeof(OutT) == 2 ? 64 : 32;          // columns of a staged group (one 128-byte output row)
                 const int cg_in = (c0 - col_lo) % CPG_IN;
-                const int t128 = (q << 5) | lane;                            // thread index inside the half
-                auto stage_block = [&](const unsigned char *base, long long bs_bytes, long long rs_bytes, int esz, int first_col) {
-                    // [128 rows][128 bytes] of a tensor shaped like the output, starting at this CTA's first row and `first_col`
-                    const int row0 = mt * MT + (int)rank * kBM;
-                    const int per_piece = 16 / esz;
+                auto commit_block = [&]() {                                  // the prefetched block into the staging block
 #pragma unroll
                     for (int it = 0; it < 8; ++it) {
                         const int idx = it * 128 + t128, rr = idx >> 3, pc = idx & 7;
-                        uint4 val = make_uint4(0, 0, 0, 0);
-                        if (row0 + rr < a.rows && first_col + pc * per_piece < a.N)
-                            val = __ldg(reinterpret_cast<const uint4 *>(base + b * bs_bytes + (long long)(row0 + rr) * rs_bytes +
-                                                                         (long long)first_col * esz + pc * 16));
-                        *reinterpret_cast<uint4 *>(stg + rr * 128 + ((pc ^ (rr & 7)) << 4)) = val;
+                        *reinterpret_cast<uint4 *>(stg + rr * 128 + ((pc ^ (rr & 7)) << 4)) = pre[it];
                     }
                     asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
                 };
+                auto fetch_next = [&]() {                                    // the block after this group, if the half has one
+                    if (c0 + 32 < col_lo + BN / 2) fetch_block(b, mt * MT + (int)rank * kBM, col + 32);
+                };
                 auto staged_done = [&]() { asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory"); };
-                if (a.tma_store && e.gate != nullptr && sizeof(OutT) == 2) {
+                if (in_gate) {
                     // one staged group of the gate (64 bfloat16 per row) serves two 32-column chunks
-                    if (cg_in == 0) stage_block((const unsigned char *)e.gate, e.gate_bs * 2, e.gate_rs * 2, 2, col);
+                    if (cg_in == 0) commit_block();
                     const unsigned char *srow = stg + row_local * 128;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -301,7 +337,7 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
 #pragma unroll
                         for (int j = 0; j < 8; ++j) v[8 * i + j] = (__bfloat162float(ge[j]) > 0.f) ? v[8 * i + j] * e.gate_scale : 0.f;
                     }
-                    if (cg_in + 32 == CPG_IN) staged_done();
+                    if (cg_in + 32 == CPG_IN) { staged_done(); fetch_next(); }
                 } else if (live && e.gate != nullptr) {
                     // pass the value where the gate tensor (same shape as the output) is positive: the backward of
                     // relu followed by dropout, whose forward output is the gate
@@ -316,8 +352,8 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                         }
                     }
                 }
-                if (a.tma_store && e.residual != nullptr && sizeof(OutT) == 4) {
-                    stage_block((const unsigned char *)e.residual, e.res_bs * 4, e.res_rs * 4, 4, col);
+                if (in_res) {
+                    commit_block();
                     const unsigned char *srow = stg + row_local * 128;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -325,6 +361,7 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                         v[4 * i] += rv.x; v[4 * i + 1] += rv.y; v[4 * i + 2] += rv.z; v[4 * i + 3] += rv.w;
                     }
                     staged_done();
+                    fetch_next();
                 } else if (live && e.residual != nullptr) {
                     const float *rp = e.residual + b * e.res_bs + (int64_t)row * e.res_rs + col;
 #pragma unroll
@@ -336,26 +373,37 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                     }
                 }
                 if (e.ce_partial != nullptr && live) {
-                    // logits as they are stored (rounded to bfloat16), classes [0, ce_classes): running max / sum of
-                    // exponentials, plain sum (label smoothing) and the target's logit
-                    float cm = ce_m;
+                    // classes [0, ce_classes): running max and sum of exponentials (base 2, on log2(e)-scaled logits), the
+                    // plain sum (label smoothing) and the target's logit.  Five instructions per element on the common path.
+                    constexpr float kL2e = 1.4426950408889634f;
+                    const int nvalid = min(32, e.ce_classes - col);             // classes in this chunk (may be <= 0 in padding)
+                    if (nvalid > 0) {
+                        float cm = ce_m;
+                        if (nvalid == 32) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
-                        if (col + i < e.ce_classes) cm = fmaxf(cm, v[i]);
-                    }
-                    if (cm > -INFINITY) {
-                        float add = 0.f;
+                            for (int i = 0; i < 32; ++i) cm = fmaxf(cm, v[i]);
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            if (col + i < e.ce_classes) {
-                                add += __expf(v[i] - cm);
-                                ce_sx += v[i];
-                                if ((long long)(col + i) == ce_target) ce_xt = v[i];
-                            }
+                            for (int i = 0; i < 32; ++i) if (i < nvalid) cm = fmaxf(cm, v[i]);
                         }
-                        ce_s = ce_s * __expf(ce_m - cm) + add;
+                        const float cm2 = cm * kL2e;
+                        float add = 0.f, sx = 0.f;
+                        if (nvalid == 32) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) { add += fast_ex2(fmaf(v[i], kL2e, -cm2)); sx += v[i]; }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) if (i < nvalid) { add += fast_ex2(fmaf(v[i], kL2e, -cm2)); sx += v[i]; }
+                        }
+                        ce_s = ce_s * fast_ex2((ce_m - cm) * kL2e) + add;
+                        ce_sx += sx;
                         ce_m = cm;
+                        const long long tc = ce_target - col;
+                        const uint32_t tmask = (tc >= 0 && tc < nvalid) ? (1u << (uint32_t)tc) : 0u;
+                        if (tmask != 0) {                                   // bit tests, not an indexed read: v stays in registers
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) ce_xt = (tmask & (1u << i)) ? v[i] : ce_xt;
+                        }
                     }
                 }
                 OutT *dst = (OutT *)a.c + b * a.c_bs + (int64_t)row * a.c_rs + col;
@@ -431,6 +479,8 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                     }
                 }
             }
+            if (a.bias != nullptr && a.partial == nullptr && !a.tma_store)      // bias_s is rewritten at the top of the next tile
+                asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
             if (a.epi.ce_partial != nullptr && row_ok)
                 *reinterpret_cast<float4 *>(a.epi.ce_partial + (((long long)b * a.rows + row) * (2 * a.n_tiles) + 2 * nt + half) * 4) =
                     make_float4(ce_m, ce_s, ce_sx, ce_xt);
@@ -525,6 +575,16 @@ static bool make_map_out(CUtensorMap *m, const void *ptr, int64_t N, int64_t row
     return encode_tiled()(m, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
                           const_cast<void *>(ptr), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Programmatic dependent launch of the products: off unless HSA_B200_PDL=1 (measured: no gain inside a captured
+// training step, where back-to-back products already start within a microsecond of each other).
+static bool pdl_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("HSA_B200_PDL");
+        return v != nullptr && v[0] == '1';
+    }();
+    return on;
 }
 
 static int sm_count() {
@@ -739,7 +799,7 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
     auto launch = [&](auto kernel, int bn) -> int {
         const int stage = kBM * 128 + (sh.two ? bn / 2 : bn) * 128;
         const int stages = stage == 49152 ? 4 : 6;
-        const size_t smem = (size_t)stages * stage + 32768 + (2 * stages + 4) * 8 + 16 + 1024;
+        const size_t smem = (size_t)stages * stage + 32768 + 1024 + (2 * stages + 4) * 8 + 16 + 1024;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "hsa_gemm: shared memory %zu: %s", smem, cudaGetErrorString(e));
         cudaLaunchConfig_t cfg{};
@@ -747,13 +807,15 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
         cfg.blockDim = dim3(kGemmThreads);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = st;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = sh.two ? 2 : 1;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
         e = cudaLaunchKernelEx(&cfg, kernel, g, ma, mb, mc);
         if (e != cudaSuccess) return fail((int)e, "hsa_gemm: launch: %s", cudaGetErrorString(e));
         return launch_status("hsa_gemm");

@@ -29,7 +29,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from . import _lib
-from .ops.gemm import DropoutSpec, gemm
+from .ops.gemm import DropoutSpec, column_sums, gemm
 
 BF16 = torch.bfloat16
 
@@ -184,7 +184,7 @@ def level_layout(N: int) -> Tuple[List[int], List[int]]:
 
 
 def _rowsum(t: torch.Tensor) -> torch.Tensor:
-    return t.reshape(-1, t.size(-1)).sum(dim=0, dtype=torch.float32)
+    return column_sums(t)
 
 
 class FusedDecoderLayerFunction(torch.autograd.Function):

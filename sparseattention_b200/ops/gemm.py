@@ -164,6 +164,23 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     return out
 
 
+def column_sums(x: torch.Tensor) -> torch.Tensor:
+    """Float32 sums over all leading dimensions of a bfloat16 tensor [..., cols] (contiguous rows): a bias gradient."""
+    lib = _lib.load()
+    cols = x.size(-1)
+    x2 = x.reshape(-1, cols)
+    if x2.stride(1) != 1 or x2.stride(0) % 8 or cols % 8 or x2.dtype != torch.bfloat16 or x2.data_ptr() % 16:
+        return x2.sum(dim=0, dtype=torch.float32)
+    rows = x2.size(0)
+    out = torch.empty(cols, dtype=torch.float32, device=x.device)
+    partial = torch.empty(int(lib.hsa_column_sums_partial_bytes(rows, cols)) // 4, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.hsa_column_sums(c_void_p(x2.data_ptr()), x2.stride(0), rows, cols, c_void_p(out.data_ptr()),
+                                 c_void_p(partial.data_ptr()), _lib.stream_ptr(x.device))
+    _lib.check(rc, "hsa_column_sums")
+    return out
+
+
 def gemm_aborts() -> int:
     """Thread blocks of hsa_gemm that gave up a bounded wait (0 in a healthy run); synchronises."""
     import ctypes

@@ -110,11 +110,13 @@ class _LinearCrossEntropy(torch.autograd.Function):
         dev = logits.device
         M, Vp = logits.shape
         scale = (grad_out.to(torch.float32) / count).reshape(1).contiguous()
-        with torch.cuda.device(dev):          # the gradient overwrites the logits in place: they are not needed again
-            rc = lib.hsa_cross_entropy_bwd(c_void_p(logits.data_ptr()), logits.stride(0), c_void_p(targets.data_ptr()),
-                                           c_void_p(lse.data_ptr()), c_void_p(scale.data_ptr()), c_void_p(logits.data_ptr()),
-                                           logits.stride(0), M, V, Vp, eps, ignore, _lib.HSA_BF16, _lib.stream_ptr(dev))
-        _lib.check(rc, "hsa_cross_entropy_bwd")
+        col_sums = torch.empty(Vp, dtype=torch.float32, device=dev)
+        partial = torch.empty(int(lib.hsa_column_sums_partial_bytes(M, Vp)) // 4, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):          # the gradient overwrites the logits in place; its column sums are the bias gradient
+            rc = lib.hsa_cross_entropy_bwd_inplace(c_void_p(logits.data_ptr()), logits.stride(0), c_void_p(targets.data_ptr()),
+                                                   c_void_p(lse.data_ptr()), c_void_p(scale.data_ptr()), M, V, Vp, eps, ignore,
+                                                   c_void_p(col_sums.data_ptr()), c_void_p(partial.data_ptr()), _lib.stream_ptr(dev))
+        _lib.check(rc, "hsa_cross_entropy_bwd_inplace")
         dlogits = logits
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
@@ -123,7 +125,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
             dw = gemm(dlogits.unsqueeze(0), xb.unsqueeze(0), a_t=True, b_t=True,
                       out_dtype=torch.float32 if wdt == torch.float32 else torch.bfloat16).to(wdt)
         if bdt is not None and ctx.needs_input_grad[2]:
-            db = dlogits.sum(dim=0, dtype=torch.float32).to(bdt)
+            db = col_sums.to(bdt)
         return dx, dw, db, None, None, None, None
 
 
