@@ -256,11 +256,13 @@ LM_VOCAB = 50257
 
 
 def run_lm(args, device, world, rank, barrier, use_dist, name, strong=False, allreduce=True, attention_cls=None,
-           graph=True, steps=None):
+           graph=True, steps=None, fused=True):
     """Training step (forward, loss, backward, gradient all-reduce, clip, AdamW) of the hierarchical LM
     on Zipf(1.1) token ids.  Per-GPU batch fixed (weak scaling) unless `strong`, which splits the config's
     batch over the ranks (global batch fixed).  `allreduce=False` leaves the collective out (to see what it
-    costs on the same ranks).  Returns whole-job tokens/s and the step's share of the tensor roofline."""
+    costs on the same ranks).  `fused=False` runs the decoder layers and the LM head op by op under autocast (library
+    products, separate element-wise kernels) instead of the library's fused nodes: the step as it was before them.
+    Returns whole-job tokens/s and the step's share of the tensor roofline."""
     import torch.distributed as dist
     from sparseattention_b200.dp import BucketedGradAverager
     from sparseattention_b200.lm import TransformerLM, lm_loss, zipf_tokens
@@ -272,6 +274,10 @@ def run_lm(args, device, world, rank, barrier, use_dist, name, strong=False, all
     torch.manual_seed(0)
     kwargs = {} if attention_cls is None else {"attention_cls": attention_cls}
     model = TransformerLM(LM_VOCAB, 512, 8, 2048, 6, dropout=0.1, window_size=16, **kwargs).to(device)
+    if not fused:
+        model.fused_head = False
+        for layer in model.layers:
+            layer.fused = False
     avg = BucketedGradAverager(model.parameters(), communicate=allreduce)
     use_graph = graph and not args.no_cuda_graph
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, fused=True, capturable=use_graph)
@@ -315,7 +321,7 @@ def run_lm(args, device, world, rank, barrier, use_dist, name, strong=False, all
            "allreduce_bytes_per_step": avg.bytes_per_step() if (world > 1 and allreduce) else 0,
            "loss_first": float(losses[0]), "loss_last": float(losses[-1]),
            "step": "fwd + label-smoothed CE + bwd + NCCL grad all-reduce + clip + AdamW, bf16 autocast",
-           "cuda_graph": runner.captured,
+           "cuda_graph": runner.captured, "fused_nodes": bool(fused and attention_cls is None),
            "roofline": {"bound": "tensor", "achieved": tflops, "peak": tf_peak, "unit": "TFLOP/s",
                         "frac": tflops / tf_peak, "peak_source": peak_kind + " (sustained bf16 matmul)",
                         "flops_per_step_per_gpu": flops_step,
@@ -433,6 +439,48 @@ def gemm_table(device, steps=20):
     return out
 
 
+def parent_tree_table(device, steps=20, B=8, N=4096, H=8, D=64):
+    """The bottom-up refresh above level 0 at the LM's shape (8 sequences of 4096 leaves, 8 heads of 64): one cooperative
+    launch per tree and direction against one projection + one attention launch per level (what it replaces)."""
+    import sparseattention_b200.fused_layer as fl
+    from sparseattention_b200.ops.gemm import gemm
+    d, M = H * D, N - 1
+    gen = torch.Generator(device=device).manual_seed(11)
+    rnd = lambda *s: torch.randn(*s, generator=gen, device=device).bfloat16()          # noqa: E731
+    QKVp, Rb, KVc, W = rnd(B, M, 3 * d), rnd(B, M, d), rnd(B, M, 2 * d), (rnd(2 * d, d) * 0.05)
+    dRf = torch.randn(B, M, d, generator=gen, device=device)
+    dRb, dQKVp, dKVc = dRf.bfloat16(), torch.empty_like(QKVp), torch.empty_like(KVc)
+    sizes, offs = fl.level_layout(N)
+    L = len(sizes)
+
+    def per_level_fwd():
+        for lvl in range(1, L):
+            po, pp, off, P = offs[lvl - 1], sizes[lvl - 1], offs[lvl], sizes[lvl]
+            gemm(Rb[:, po:po + pp], W, out=KVc[:, po:po + pp])
+            sl = QKVp[:, off:off + P]
+            fl._parent_fwd(sl[..., :d], sl[..., d:2 * d], sl[..., 2 * d:], KVc[:, po:po + pp, :d], KVc[:, po:po + pp, d:],
+                           Rb[:, off:off + P], H)
+
+    def per_level_bwd():
+        for lvl in range(L - 1, 0, -1):
+            po, pp, off, P = offs[lvl - 1], sizes[lvl - 1], offs[lvl], sizes[lvl]
+            sl, dsl, dkv = QKVp[:, off:off + P], dQKVp[:, off:off + P], dKVc[:, po:po + pp]
+            fl._parent_bwd(dRb[:, off:off + P], sl[..., :d], sl[..., d:2 * d], sl[..., 2 * d:], KVc[:, po:po + pp, :d],
+                           KVc[:, po:po + pp, d:], dsl[..., :d], dsl[..., d:2 * d], dsl[..., 2 * d:], dkv[..., :d], dkv[..., d:], H)
+            gemm(dkv, W, b_t=True, out=dRf[:, po:po + pp], accumulate=True, copy_bf16=dRb[:, po:po + pp])
+
+    out = {"shape": {"B": B, "N": N, "H": H, "D": D, "levels_fused": L - 1}}
+    for name, fn, launches in (
+            ("parent_tree_fwd", lambda: fl._parent_tree_fwd(QKVp, Rb, KVc, W, N, H, 1, None), 1),
+            ("per_level_fwd", per_level_fwd, 2 * (L - 1)),
+            ("parent_tree_bwd", lambda: fl._parent_tree_bwd(QKVp, KVc, dRf, dRb, dQKVp, dKVc, W, N, H, 1, None), 1),
+            ("per_level_bwd", per_level_bwd, 2 * (L - 1))):
+        ms = time_cuda(fn, steps, 3, lambda: None) / steps
+        out[name] = {"ms": ms, "launches": launches}
+    out["status_word"] = fl.parent_tree_status(fl._parent_tree_fwd(QKVp, Rb, KVc, W, N, H, 1, None))
+    return out
+
+
 def run_only(args):
     """One kernel loop on the chosen workload (what profiler captures are taken from)."""
     torch.cuda.set_device(0)
@@ -440,11 +488,14 @@ def run_only(args):
     if args.only == "gemm":
         emit({"only": "gemm", "products": gemm_table(device, max(3, min(args.steps, 20)))})
         return
+    if args.only == "parent_tree":
+        emit({"only": "parent_tree", **parent_tree_table(device, max(3, min(args.steps, 20)))})
+        return
     if args.only == "reference_triton":
         emit(reference_triton_child(args, device))
         return
     if args.only == "lm":
-        out = run_lm(args, device, 1, 0, lambda: None, False, args.lm, graph=not args.no_cuda_graph)
+        out = run_lm(args, device, 1, 0, lambda: None, False, args.lm, graph=not args.no_cuda_graph, fused=not args.lm_eager)
         emit({"only": "lm", **out})
         return
     loops, _ = kernel_loops(args.workload, device)
@@ -671,6 +722,17 @@ def run_ours(args):
         state.clear()
         del loops
         torch.cuda.empty_cache()
+        if world == 1:
+            extras["parent_tree"] = parent_tree_table(device, bsteps)
+            table = gemm_table(device, 10)
+            extras["tcgen05_products"] = {
+                "note": "the dense products of one LM step (32768 tokens) on the library's tcgen05 kernel; TFLOP/s, and the "
+                        "vendor library (torch.matmul) on the same shapes beside it",
+                "products": [{"product": r["product"], "M": r["M"], "N": r["N"], "K": r["K"],
+                              **{k: {"ours_tflops": round(r[k]["ours_tflops"], 1), "library_tflops": round(r[k]["library_tflops"], 1),
+                                     "frac_of_sustained_peak": round(r[k]["frac_of_sustained_peak"], 3)} for k in ("fwd", "dx", "dw")}}
+                             for r in table]}
+            torch.cuda.empty_cache()
 
     # ---- the model that calls the layer: data-parallel LM training step (all ranks) ---------------
     if not args.no_lm:
@@ -685,6 +747,11 @@ def run_ours(args):
             if LM_CONFIGS[args.lm]["batch"] % world == 0:
                 # secondary line: the same global batch as one GPU, split over the ranks
                 extras["lm_train_strong"] = run_lm(args, device, world, rank, barrier, use_dist, args.lm, strong=True)
+        if world == 1:
+            # the same step with the decoder layers and the head run op by op (library products, separate element-wise
+            # kernels), i.e. without the fused nodes: what they buy
+            eager = run_lm(args, device, world, rank, barrier, use_dist, args.lm, fused=False)
+            lm["ms_per_step_unfused"] = eager["ms_per_step"]
         other = "lm_8x2048" if args.lm != "lm_8x2048" else "lm_8x4096"
         extras["lm_train_" + other[3:]] = run_lm(args, device, world, rank, barrier, use_dist, other)
         extras["lm_scaling"] = {"n_gpus": world, "tokens_per_s": lm["tokens_per_s"], "ms_per_step": lm["ms_per_step"],
@@ -773,7 +840,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="layer_n4096", choices=sorted(WORKLOADS))
-    ap.add_argument("--only", default=None, choices=["fwd", "bwd", "parents", "parents_bwd", "lm", "reference_triton", "gemm"],
+    ap.add_argument("--only", default=None, choices=["fwd", "bwd", "parents", "parents_bwd", "lm", "reference_triton", "gemm", "parent_tree"],
                     help="run one kernel loop (or the LM step, or the reference's Triton package) and print a short JSON line")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--sustained-seconds", type=float, default=2.5)
@@ -784,6 +851,7 @@ def main():
     ap.add_argument("--no-reference-triton", action="store_true")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch the LM step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--lm", default="lm_8x4096", choices=sorted(LM_CONFIGS))
+    ap.add_argument("--lm-eager", action="store_true", help="with --only lm: layers and head op by op (library products) instead of the fused nodes")
     ap.add_argument("--sweep", action="store_true", help="print the forward sweep over N and batch instead of the JSON line")
     args = ap.parse_args()
     if args.sweep:

@@ -275,7 +275,7 @@ def lm_loss(model: "TransformerLM", tokens: torch.Tensor, label_smoothing: float
     (the reference's loader and criterion, Pretrain.py:181-194, 514), computed by the library's
     cross-entropy kernel straight on the padded logits."""
     if (tokens.is_cuda and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16
-            and model.d_model % 8 == 0):
+            and model.d_model % 8 == 0 and getattr(model, "fused_head", True)):
         # bf16 autocast: LM head and loss in one pass (tcgen05 product whose epilogue keeps the softmax statistics)
         hidden = model(tokens[:, :-1], hidden_only=True)
         return linear_cross_entropy(hidden.reshape(-1, hidden.size(-1)), model.fc_out.weight, model.fc_out.bias,
