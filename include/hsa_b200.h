@@ -291,7 +291,9 @@ int hsa_layer_norm_bwd(const void *x, const void *dy, const float *gamma, const 
  * Dropout masks are a pure function of (*rng_state, site, element id), element id = position in the logical
  * [batches, drop_rows_total, N] tensor (this product writes rows drop_row_offset .. of it); hsa_dropout_apply
  * regenerates them.  drop_site1 != 0 applies a second, independent mask (values dropped twice).
- * drop_threshold = p * 2^32, drop_scale = 1/(1-p) (squared with two masks).  A zeroed struct is "no tail".
+ * drop_threshold = p * 2^32 (its upper 16 bits are compared: p is honoured to 2^-16), drop_scale = 1/(1-p) (squared with
+ * two masks).  drop_col_begin and drop_col_end are multiples of 32 (drop_col_end may also be N); the logical tensor has at
+ * most 2^33 elements.  A zeroed struct is "no tail".
  */
 typedef struct hsa_gemm_epilogue {
     int relu;

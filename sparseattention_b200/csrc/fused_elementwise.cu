@@ -23,6 +23,7 @@ dropout_apply_kernel(DropArgs a) {
     const int vec_per_row = a.ncols / 8;
     const long long total = (long long)a.batches * a.rows * vec_per_row;
     const unsigned long long key = *a.rng_state;
+    const uint32_t salt0 = dropout_salt(key, a.site0, 0), salt1 = dropout_salt(key, a.site1, 0);
     for (long long idx = (long long)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (long long)gridDim.x * 256) {
         const int c8 = (int)(idx % vec_per_row);
         const long long br = idx / vec_per_row;
@@ -43,11 +44,15 @@ dropout_apply_kernel(DropArgs a) {
                                        (unsigned long long)a.N + (unsigned long long)(col + a.col_shift);
         uint4 o;
         __nv_bfloat162 *p = reinterpret_cast<__nv_bfloat162 *>(&o);
+        if ((id0 & 1ull) == 0 && id0 + 8 <= kDropoutRunMaxElems) {
+            dropout_run(v, salt0, salt1, a.site1 != 0, id0, a.threshold, a.scale);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            bool keep = dropout_keep(key, a.site0, id0 + i, a.threshold);
-            if (a.site1 != 0) keep = keep && dropout_keep(key, a.site1, id0 + i, a.threshold);
-            v[i] = keep ? v[i] * a.scale : 0.f;
+            for (int i = 0; i < 8; ++i) {
+                bool keep = dropout_keep(key, a.site0, id0 + i, a.threshold);
+                if (a.site1 != 0) keep = keep && dropout_keep(key, a.site1, id0 + i, a.threshold);
+                v[i] = keep ? v[i] * a.scale : 0.f;
+            }
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);

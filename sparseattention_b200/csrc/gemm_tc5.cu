@@ -12,7 +12,13 @@
 //   warps 2-9 epilogue: tcgen05.ld of the 128 x BN float32 accumulator (a thread owns one row and half of its
 //            columns), bias and the fused tail, conversion, 16-byte global stores; two accumulators (2 x BN columns of
 //            tensor memory) alternate, so the epilogue of tile i overlaps the main loop of tile i+1.  With the short
-//            reductions of this model (K = 512: 2.9 us of MMA per tile) four epilogue warps could not keep up
+//            reductions of this model (K = 512: 2.9 us of MMA per tile) four epilogue warps could not keep up.
+//            Measured on this kernel with K = 512: the main loop alone sustains 1.3-1.6 PFLOP/s; reading the accumulators
+//            costs 6-8 % of that; conversion, staging and barriers next to nothing; what remains (to 0.9-1.0 PFLOP/s) is
+//            the output's way to L2 (2 TB/s of writes), whichever instruction carries it (bulk copies from shared memory
+//            are the fastest of three forms tried).  So the epilogue is kept lean: a second instantiation without the
+//            optional tail, dropout decisions two per hash, and two staging blocks per column half so that a bulk store
+//            drains while the next group is converted
 // Operands sit in shared memory as 128-byte rows with the TMA unit's 128-byte swizzle, which is one of the
 // canonical tcgen05 operand layouts both for K-major tiles ([row][64 k]) and for MN-major tiles ([k][64 rows]);
 // so A and B may each be given as [rows, K] or transposed as [K, rows] without a transposing copy: the three
@@ -52,6 +58,7 @@ struct GemmArgs {
 
 __device__ unsigned int g_gemm_aborts = 0;
 
+
 __device__ __forceinline__ float fast_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -62,7 +69,10 @@ __device__ __forceinline__ float fast_ex2(float x) {
 // own 128 rows of A and half of the B tile, so a stage is 32 KB instead of 48 KB per 128 output rows and every byte
 // fetched from L2 feeds twice the arithmetic.  With this model's short reductions (K = 512) the single-CTA form is
 // bound by L2 bandwidth (85 flop per byte staged), not by the tensor pipe.
-template <int BN, bool A_MN, bool B_MN, typename OutT, bool TWO>
+// FULL: the epilogue carries the optional element-wise tail (dropout, gate, residual, second copy, cross-entropy
+// statistics).  Products without one run the instantiation that has none of that code: the epilogue loop is the
+// kernel's critical path with short reductions, and its instruction footprint matters.
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool TWO, bool FULL>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_c) {
@@ -71,16 +81,16 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
     constexpr int MT = TWO ? 2 * kBM : kBM;            // rows of a tile
     constexpr int A_BYTES = kBM * 128, B_BYTES = B_ROWS * 128;
     constexpr int STAGE = A_BYTES + B_BYTES;
-    constexpr int STAGES = STAGE == 49152 ? 4 : 6;
+    constexpr int STAGES = STAGE == 49152 ? 3 : (STAGE == 32768 ? 5 : 6);
     constexpr uint32_t IDESC = instr_desc(MT, BN, true, A_MN, B_MN);
     const uint32_t rank = TWO ? cluster_ctarank() : 0;  // 0 = the CTA that issues the MMAs
     const int unit = TWO ? blockIdx.x / 2 : blockIdx.x, nunits = TWO ? gridDim.x / 2 : gridDim.x;
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
-    unsigned char *staging = smem + (size_t)STAGES * STAGE;           // 2 x 16 KB: one block of output rows per column half
-    float *bias_s = reinterpret_cast<float *>(staging + 32768);        // the tile's bias values, 128 per column half
-    unsigned long long *bars = reinterpret_cast<unsigned long long *>(staging + 32768 + 1024);
+    unsigned char *staging = smem + (size_t)STAGES * STAGE;           // 2 x 2 x 16 KB: two blocks of output rows per column half
+    float *bias_s = reinterpret_cast<float *>(staging + 65536);        // the tile's bias values, 128 per column half
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(staging + 65536 + 1024);
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -209,12 +219,14 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
         const int col_lo = ((warp - 2) >> 2) * (BN / 2);   // ... and the half of the tile's columns it owns
         int acc = 0; uint32_t acc_ph = 0;
         bool ok = true;
-        const unsigned long long drop_key = a.epi.rng_state != nullptr ? *a.epi.rng_state : 0ull;
+        uint32_t group = 0;                                // staged groups handed to the copy engine so far (this half)
+        const unsigned long long drop_key = (FULL && a.epi.rng_state != nullptr) ? *a.epi.rng_state : 0ull;
+        const uint32_t drop_salt0 = dropout_salt(drop_key, a.epi.drop_site0, 0), drop_salt1 = dropout_salt(drop_key, a.epi.drop_site1, 0);
         // Gate / residual blocks ([128 rows][128 bytes] of a tensor shaped like the output) are fetched one block AHEAD into
         // registers, 8 threads per row (whole lines), so their latency hides behind the previous block's work; the first
         // block of a tile is requested before the accumulator is even waited for.
-        const bool in_gate = a.tma_store && a.epi.gate != nullptr && sizeof(OutT) == 2;
-        const bool in_res = a.tma_store && a.epi.residual != nullptr && sizeof(OutT) == 4;
+        const bool in_gate = FULL && a.tma_store && a.epi.gate != nullptr && sizeof(OutT) == 2;
+        const bool in_res = FULL && a.tma_store && a.epi.residual != nullptr && sizeof(OutT) == 4;
         const int t128 = ((warp & 3) << 5) | lane;                           // thread index inside the column half
         uint4 pre[8];
         auto fetch_block = [&](int bb, int row0, int first_col) {
@@ -256,16 +268,23 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
             // cross-entropy statistics of this thread's row over its half of the tile's columns (when asked for)
             float ce_m = -INFINITY, ce_s = 0.f, ce_sx = 0.f, ce_xt = 0.f;
             long long ce_target = -1;
-            if (a.epi.ce_partial != nullptr && row_ok) ce_target = a.epi.ce_targets[(long long)b * a.rows + row];
+            if (FULL && a.epi.ce_partial != nullptr && row_ok) ce_target = a.epi.ce_targets[(long long)b * a.rows + row];
             const int half = (warp - 2) >> 2;                 // which half of the tile's columns
             const int row_local = q * 32 + lane;              // row inside this CTA's 128 rows
-            unsigned char *stg = staging + half * 16384;      // [128 rows][128 B], 128-byte swizzle, for the TMA stores
+            // [128 rows][128 B] blocks, 128-byte swizzle, for the TMA stores: two per half, used in turn, so that the copy
+            // engine reads one while the next group is converted into the other
+            unsigned char *stg = staging + half * 32768 + (group & 1) * 16384;
 #pragma unroll 1
             for (int c0 = col_lo; c0 < col_lo + BN / 2; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tbase + c0, r);
                 tmem_ld_wait();
                 const int col = nt * BN + c0;
+                if (a.tma_store && (c0 - col_lo) % (sizeof(OutT) == 2 ? 64 : 32) == 0) {
+                    // a new staged group: its block is free once the store issued from it two groups ago has read it, which
+                    // the issuing thread waited for right after handing over the group in between
+                    asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
+                }
                 if (a.partial != nullptr) {
                     // split-K: the raw float32 tile goes to this split's slab (padded to whole tiles: no masks)
                     float *dst = a.partial + ((size_t)sp * a.batches * a.m_tiles * MT + ((size_t)b * a.m_tiles * MT + row)) *
@@ -294,20 +313,12 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
                     }
-                    if (e.rng_state != nullptr && col + 32 > e.drop_col_begin && col < e.drop_col_end) {
+                    if (FULL && e.rng_state != nullptr && col >= e.drop_col_begin && col < e.drop_col_end) {   // ranges are whole chunks
                         // dropout on columns [drop_col_begin, drop_col_end): element id = (batch, row, column) of the logical
                         // [batches, drop_rows_total, N] tensor this product writes a row range of
-                        const unsigned long long key = drop_key;
                         const unsigned long long id0 = ((unsigned long long)b * e.drop_rows_total + (unsigned long long)(row + e.drop_row_offset)) *
                                                        (unsigned long long)a.N + (unsigned long long)col;
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            if (col + i >= e.drop_col_begin && col + i < e.drop_col_end) {
-                                bool keep = dropout_keep(key, e.drop_site0, id0 + i, e.drop_threshold);
-                                if (e.drop_site1 != 0) keep = keep && dropout_keep(key, e.drop_site1, id0 + i, e.drop_threshold);
-                                v[i] = keep ? v[i] * e.drop_scale : 0.f;
-                            }
-                        }
+                        dropout_run(v, drop_salt0, drop_salt1, e.drop_site1 != 0, id0, e.drop_threshold, e.drop_scale);
                     }
                 }
                 // Gate and residual blocks are fetched by the four warps of this half together, 8 threads per 128-byte row
@@ -338,7 +349,7 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                         for (int j = 0; j < 8; ++j) v[8 * i + j] = (__bfloat162float(ge[j]) > 0.f) ? v[8 * i + j] * e.gate_scale : 0.f;
                     }
                     if (cg_in + 32 == CPG_IN) { staged_done(); fetch_next(); }
-                } else if (live && e.gate != nullptr) {
+                } else if (FULL && live && e.gate != nullptr) {
                     // pass the value where the gate tensor (same shape as the output) is positive: the backward of
                     // relu followed by dropout, whose forward output is the gate
                     const __nv_bfloat16 *gp = (const __nv_bfloat16 *)e.gate + b * e.gate_bs + (int64_t)row * e.gate_rs + col;
@@ -362,7 +373,7 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                     }
                     staged_done();
                     fetch_next();
-                } else if (live && e.residual != nullptr) {
+                } else if (FULL && live && e.residual != nullptr) {
                     const float *rp = e.residual + b * e.res_bs + (int64_t)row * e.res_rs + col;
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
@@ -372,7 +383,7 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                         }
                     }
                 }
-                if (e.ce_partial != nullptr && live) {
+                if (FULL && e.ce_partial != nullptr && live) {
                     // classes [0, ce_classes): running max and sum of exponentials (base 2, on log2(e)-scaled logits), the
                     // plain sum (label smoothing) and the target's logit.  Five instructions per element on the common path.
                     constexpr float kL2e = 1.4426950408889634f;
@@ -419,7 +430,7 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                         }
                     }
                 };
-                if (e.ce_partial != nullptr && e.ce_skip_store) {
+                if (FULL && e.ce_partial != nullptr && e.ce_skip_store) {
                     // loss only: the logits are never written
                 } else if (a.tma_store) {
                     // Rows leave through the copy engine: the 4 warps of this half park a [128 rows][128 B] block in shared
@@ -452,12 +463,13 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                             asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];\n"
                                          ::"l"(&map_c), "r"(gcol), "r"(mt * MT + (int)rank * kBM), "r"(b), "r"(smem_addr(stg)) : "memory");
                             asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
-                            asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+                            asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");   // the previous group's block is free
                         }
-                        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
+                        ++group;
+                        stg = staging + half * 32768 + (group & 1) * 16384;
                     }
                     if constexpr (sizeof(OutT) == 4) {
-                        if (live && e.copy_bf16 != nullptr)
+                        if (FULL && live && e.copy_bf16 != nullptr)
                             store_bf16((__nv_bfloat16 *)e.copy_bf16 + b * e.copy_bs + (int64_t)row * e.copy_rs + col);
                     }
                 } else if (live) {
@@ -474,14 +486,14 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                                 *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                             }
                         }
-                        if (e.copy_bf16 != nullptr)
+                        if (FULL && e.copy_bf16 != nullptr)
                             store_bf16((__nv_bfloat16 *)e.copy_bf16 + b * e.copy_bs + (int64_t)row * e.copy_rs + col);
                     }
                 }
             }
             if (a.bias != nullptr && a.partial == nullptr && !a.tma_store)      // bias_s is rewritten at the top of the next tile
                 asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
-            if (a.epi.ce_partial != nullptr && row_ok)
+            if (FULL && a.epi.ce_partial != nullptr && row_ok)
                 *reinterpret_cast<float4 *>(a.epi.ce_partial + (((long long)b * a.rows + row) * (2 * a.n_tiles) + 2 * nt + half) * 4) =
                     make_float4(ce_m, ce_s, ce_sx, ce_xt);
             fence_before_sync();
@@ -492,6 +504,7 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
             }
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
+        if (a.tma_store && q == 0 && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -743,6 +756,10 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
                       "hsa_gemm_ex: bad cross-entropy description (bfloat16 logits, targets, 1 <= classes <= N)");
         HSA_CHECK_ARG(e.rng_state == nullptr || (e.drop_col_begin >= 0 && e.drop_col_end <= N && e.drop_site0 != 0 && e.drop_rows_total >= rows),
                       "hsa_gemm_ex: bad dropout description");
+        HSA_CHECK_ARG(e.rng_state == nullptr || (e.drop_col_begin % 32 == 0 && (e.drop_col_end % 32 == 0 || e.drop_col_end == N)),
+                      "hsa_gemm_ex: the dropout column range starts and ends on multiples of 32 (or ends with the last column)");
+        HSA_CHECK_ARG(e.rng_state == nullptr || (unsigned long long)batches * (unsigned long long)e.drop_rows_total * (unsigned long long)N <= kDropoutRunMaxElems,
+                      "hsa_gemm_ex: the tensor the dropout ids refer to has more than 2^33 elements");
     }
     // K runs over rows of the stored tensors when an operand is transposed; a transposed A carries the batch dimension
     // in K (the weight gradient sums over every row of every batch entry)
@@ -798,8 +815,8 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
 
     auto launch = [&](auto kernel, int bn) -> int {
         const int stage = kBM * 128 + (sh.two ? bn / 2 : bn) * 128;
-        const int stages = stage == 49152 ? 4 : 6;
-        const size_t smem = (size_t)stages * stage + 32768 + 1024 + (2 * stages + 4) * 8 + 16 + 1024;
+        const int stages = stage == 49152 ? 3 : (stage == 32768 ? 5 : 6);
+        const size_t smem = (size_t)stages * stage + 65536 + 1024 + (2 * stages + 4) * 8 + 16 + 1024;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "hsa_gemm: shared memory %zu: %s", smem, cudaGetErrorString(e));
         cudaLaunchConfig_t cfg{};
@@ -822,17 +839,21 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
     };
     const bool f32 = out_dtype == HSA_F32 || g.partial != nullptr;
     int rc;
-#define HSA_GEMM_CASE(BNV, AMN, BMN)                                                                                   \
-    (sh.two ? (f32 ? launch(gemm_tc5_kernel<BNV, AMN, BMN, float, true>, BNV)                                          \
-                   : launch(gemm_tc5_kernel<BNV, AMN, BMN, __nv_bfloat16, true>, BNV))                                 \
-            : (f32 ? launch(gemm_tc5_kernel<BNV, AMN, BMN, float, false>, BNV)                                         \
-                   : launch(gemm_tc5_kernel<BNV, AMN, BMN, __nv_bfloat16, false>, BNV)))
+    const bool full = epilogue != nullptr && (epilogue->rng_state != nullptr || epilogue->gate != nullptr || epilogue->residual != nullptr ||
+                                              epilogue->copy_bf16 != nullptr || epilogue->ce_partial != nullptr);
+#define HSA_GEMM_CASE2(BNV, AMN, BMN, FULLV)                                                                           \
+    (sh.two ? (f32 ? launch(gemm_tc5_kernel<BNV, AMN, BMN, float, true, FULLV>, BNV)                                   \
+                   : launch(gemm_tc5_kernel<BNV, AMN, BMN, __nv_bfloat16, true, FULLV>, BNV))                          \
+            : (f32 ? launch(gemm_tc5_kernel<BNV, AMN, BMN, float, false, FULLV>, BNV)                                  \
+                   : launch(gemm_tc5_kernel<BNV, AMN, BMN, __nv_bfloat16, false, FULLV>, BNV)))
+#define HSA_GEMM_CASE(BNV, AMN, BMN) (full ? HSA_GEMM_CASE2(BNV, AMN, BMN, true) : HSA_GEMM_CASE2(BNV, AMN, BMN, false))
     if (BN == 256) {
         rc = a_layout ? HSA_GEMM_CASE(256, true, true) : (b_layout ? HSA_GEMM_CASE(256, false, true) : HSA_GEMM_CASE(256, false, false));
     } else {
         rc = a_layout ? HSA_GEMM_CASE(128, true, true) : (b_layout ? HSA_GEMM_CASE(128, false, true) : HSA_GEMM_CASE(128, false, false));
     }
 #undef HSA_GEMM_CASE
+#undef HSA_GEMM_CASE2
     if (rc != 0 || splits == 1) return rc;
     const size_t slab = (size_t)out_batches * g.m_tiles * sh.MT * g.n_tiles * BN;
     const size_t work = (size_t)out_batches * rows * (N / 4);

@@ -197,9 +197,7 @@ parent_tree_kernel(const TreeArgs a, const __grid_constant__ CUtensorMap map_a, 
                         if (a.rng != nullptr && col >= d) {                 // the value half: dropout, ids of the [B, M, 2d] tensor
                             const unsigned long long key = *a.rng;
                             const unsigned long long id0 = ((unsigned long long)b * M + (unsigned long long)(po + r)) * (2ull * d) + col;
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                v[i] = dropout_keep(key, a.site, id0 + i, a.threshold) ? v[i] * a.drop_scale : 0.f;
+                            dropout_run(v, dropout_salt(key, a.site, 0), 0u, false, id0, a.threshold, a.drop_scale);
                         }
                         __nv_bfloat16 *dst = a.C + b * a.c_bs + (int64_t)(po + r) * a.c_rs + col;
 #pragma unroll
@@ -309,9 +307,7 @@ parent_tree_kernel(const TreeArgs a, const __grid_constant__ CUtensorMap map_a, 
                         if (a.rng != nullptr) {
                             const unsigned long long key = *a.rng;
                             const unsigned long long id0 = ((unsigned long long)b * M + (unsigned long long)crow) * (2ull * d) + d + hoff + 8 * g;
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                t.v[0][i] = dropout_keep(key, a.site, id0 + i, a.threshold) ? t.v[0][i] * a.drop_scale : 0.f;
+                            dropout_run(t.v[0], dropout_salt(key, a.site, 0), 0u, false, id0, a.threshold, a.drop_scale);
                         }
                         t.store(dvc + crow * a.dc_rs, g, D / 8);
                     };
@@ -394,6 +390,8 @@ static int tree_check(const char *what, int B, int N, int H, int D, int start) {
                   what, B, N, H, D);
     HSA_CHECK_ARG((H * D) % 256 == 0, "%s: the model width H*D = %d must be a multiple of 256", what, H * D);
     HSA_CHECK_ARG(start >= 1 && start < ilog2((unsigned)N), "%s: start_level %d outside [1, log2 N)", what, start);
+    HSA_CHECK_ARG((unsigned long long)B * (unsigned long long)(N - 1) * 2ull * (unsigned long long)(H * D) <= kDropoutRunMaxElems,
+                  "%s: more than 2^33 child K/V elements", what);
     return 0;
 }
 
