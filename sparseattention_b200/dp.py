@@ -2,9 +2,10 @@
 
 The reference has no multi-process training (it only wraps the model in nn.DataParallel,
 hierarchical_attention_project/Hierarchical_Transformer_Triton_WikiText103.py:619-624); this is the
-batch-sharded equivalent.  All gradients live in a few flat buckets (parameters' .grad are views into
-them), filled by autograd in reverse layer order; a bucket is all-reduced asynchronously the moment
-its last gradient has been accumulated, so the transfers overlap the rest of the backward.
+batch-sharded equivalent.  Gradients are gathered into a few flat buckets in reverse layer order (one
+multi-tensor copy per bucket when its last gradient has arrived); a bucket is all-reduced asynchronously at
+that moment, so the transfers overlap the rest of the backward, and afterwards the parameters' .grad are
+views into the averaged buckets.
 """
 from __future__ import annotations
 
@@ -22,6 +23,9 @@ class BucketedGradAverager:
         self.group = process_group
         self.world = dist.get_world_size(process_group) if (dist.is_initialized() and communicate) else 1
         self.params = [p for p in params if p.requires_grad]
+        # the flat buckets are used whenever the job has more than one rank (also with communicate=False, so that only
+        # the collective itself is left out of that comparison); a single process keeps autograd's own gradient tensors
+        self.bucketed = dist.is_initialized() and dist.get_world_size(process_group) > 1
         backend = dist.get_backend(process_group) if dist.is_initialized() else "none"
         self._avg_op = backend == "nccl"            # gloo has no AVG: sum, then scale
         # buckets in reverse registration order = roughly the order gradients become ready
@@ -43,31 +47,35 @@ class BucketedGradAverager:
 
     def _close(self, plist):
         flat = torch.zeros(sum(p.numel() for p in plist), dtype=plist[0].dtype, device=plist[0].device)
-        off = 0
+        views, off = [], 0
         for p in plist:
-            p.grad = flat[off: off + p.numel()].view_as(p)
+            views.append(flat[off: off + p.numel()].view_as(p))
             off += p.numel()
-        self.buckets.append({"params": list(plist), "flat": flat, "pending": len(plist), "views": [p.grad for p in plist]})
+        self.buckets.append({"params": list(plist), "flat": flat, "pending": len(plist), "views": views})
 
     def _make_hook(self, bi: int):
         def hook(param):
             b = self.buckets[bi]
             b["pending"] -= 1
-            if b["pending"] == 0 and self.world > 1:
-                op = dist.ReduceOp.AVG if self._avg_op else dist.ReduceOp.SUM
-                self._handles.append((dist.all_reduce(b["flat"], op=op, group=self.group, async_op=True), bi))
+            if b["pending"] == 0 and self.bucketed:
+                # the bucket's gradients are complete: one multi-tensor copy into the flat buffer, then its all-reduce
+                torch._foreach_copy_(b["views"], [p.grad for p in b["params"]])
+                if self.world > 1:
+                    op = dist.ReduceOp.AVG if self._avg_op else dist.ReduceOp.SUM
+                    self._handles.append((dist.all_reduce(b["flat"], op=op, group=self.group, async_op=True), bi))
         return hook
 
     def zero_grad(self):
-        """Clear the flat buckets and re-point .grad at them (an optimizer may have replaced them)."""
+        """Drop last step's gradients.  Autograd then hands each parameter its gradient as a fresh tensor (no zero fill,
+        no `grad += new` kernel per parameter); the flat buckets are filled by one copy per bucket when it is complete."""
         for b in self.buckets:
-            b["flat"].zero_()
             b["pending"] = len(b["params"])
-            for p, v in zip(b["params"], b["views"]):
-                p.grad = v
+        for p in self.params:
+            p.grad = None
 
     def finish(self):
-        """Wait for the outstanding all-reduces of this backward; gradients are then averaged."""
+        """Wait for the outstanding all-reduces of this backward; `.grad` of every parameter then is the averaged
+        gradient (a view into its bucket when the job has more than one rank)."""
         for h, bi in self._handles:
             h.wait()
             if not self._avg_op and self.world > 1:
@@ -76,6 +84,9 @@ class BucketedGradAverager:
         for b in self.buckets:
             if b["pending"] != 0 and self.world > 1:
                 raise RuntimeError("a parameter received no gradient this step; its bucket was never reduced")
+            if self.bucketed and b["pending"] == 0:
+                for p, v in zip(b["params"], b["views"]):
+                    p.grad = v
 
     def bytes_per_step(self) -> int:
         return sum(b["flat"].numel() * b["flat"].element_size() for b in self.buckets)
