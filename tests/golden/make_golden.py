@@ -1,7 +1,6 @@
 """Generate the golden vectors under tests/golden/ from the reference project itself.
 
-Run where the reference checkout is mounted (default /root/reference, override with
-HSA_REFERENCE_DIR):
+Run where the reference checkout is mounted (its directory: HSA_REFERENCE_DIR, default `REF` below):
 
     python tests/golden/make_golden.py
 
