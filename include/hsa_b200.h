@@ -377,6 +377,18 @@ size_t hsa_column_sums_partial_bytes(long long rows, int cols);
 int hsa_column_sums(const void *x, long long row_stride, long long rows, int cols, float *out, float *partial, void *stream);
 
 /*
+ * out = bfloat16(mask * in) for a float32 matrix [rows, cols] with contiguous rows, and col_sums[c] = the float32 sum
+ * over rows of what was written: the gradient's way through a residual dropout
+ * (hierarchical_attention_project/Hierarchical_Transformer_Pretrain.py:406,419,424) and the bias gradient of the
+ * projection under it, which autograd computes in three passes.  The mask is that of hsa_gemm_ex / hsa_dropout_apply
+ * for a logical tensor [rows, cols] (element id r * cols + c, same rng_state value, sites, threshold); rng_state null:
+ * no mask (a cast).  cols a multiple of 8; `partial`: hsa_column_sums_partial_bytes(rows, cols) bytes.
+ */
+int hsa_dropout_cast_colsum(const float *in, long long in_row_stride, void *out, long long out_row_stride, long long rows,
+                            int cols, const unsigned long long *rng_state, unsigned int site0, unsigned int site1,
+                            unsigned int threshold, float scale, float *col_sums, float *partial, void *stream);
+
+/*
  * hsa_cross_entropy_bwd for bfloat16 logits IN PLACE (the logits are overwritten by their gradient) together with the
  * column sums of that gradient, col_sums [Vp] float32: the bias gradient of the LM head, which otherwise costs another
  * pass over the [tokens, vocabulary] matrix.  `partial`: hsa_column_sums_partial_bytes(rows, Vp) bytes.

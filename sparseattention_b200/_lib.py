@@ -86,6 +86,8 @@ SIGNATURES = {
     "hsa_layer_norm_bwd_mixed": (c_int, [c_void_p] * 10 + [c_int64, c_int, c_void_p]),
     "hsa_column_sums_partial_bytes": (c_size_t, [ctypes.c_longlong, c_int]),
     "hsa_column_sums": (c_int, [c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_int, c_void_p, c_void_p, c_void_p]),
+    "hsa_dropout_cast_colsum": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_int, c_void_p,
+                                        ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, c_float, c_void_p, c_void_p, c_void_p]),
     "hsa_cross_entropy_bwd_inplace": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int,
                                               c_float, ctypes.c_longlong, c_void_p, c_void_p, c_void_p]),
     "hsa_dropout_apply": (c_int, [V, c_int, V, c_int, c_int, c_int, c_int, ctypes.c_longlong, ctypes.c_longlong,

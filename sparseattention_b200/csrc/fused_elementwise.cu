@@ -64,6 +64,9 @@ dropout_apply_kernel(DropArgs a) {
 // out[c] = sum over rows of x[r, c] (bias gradients).  A thread owns 8 consecutive columns and every fourth row of a block
 // of kCsRows rows; the four row lanes are combined through shared memory, blocks by a second kernel in block order.
 constexpr int kCsRows = 256;
+// The narrow matrices of the layers (a few hundred columns) take smaller blocks, or too few of them are in flight
+constexpr int kCsRowsNarrow = 64;
+__host__ __device__ inline int cs_rows_per_block(int cols) { return cols <= 4096 ? kCsRowsNarrow : kCsRows; }
 
 // `rows4(r, n, col, v)` yields the values of rows r, r+4, .. (n <= 4 of them) at columns col..col+7, having issued all
 // of their loads before anything depends on one (one load in flight per thread leaves HBM mostly idle).
@@ -97,8 +100,9 @@ __device__ __forceinline__ void colsum_block(int rows_here, int cols, int col0, 
 
 __global__ void __launch_bounds__(256)
 column_sums_kernel(const __nv_bfloat16 *__restrict__ x, int64_t row_stride, int64_t rows, int cols, float *__restrict__ partial) {
-    const int64_t r0 = (int64_t)blockIdx.y * kCsRows;
-    const int rows_here = (int)((rows - r0) < kCsRows ? (rows - r0) : kCsRows);
+    const int rpb = cs_rows_per_block(cols);
+    const int64_t r0 = (int64_t)blockIdx.y * rpb;
+    const int rows_here = (int)((rows - r0) < rpb ? (rows - r0) : rpb);
     colsum_block(rows_here, cols, blockIdx.x * 512, partial + (int64_t)blockIdx.y * cols, [&](int r, int n, int col, float (&v)[4][8]) {
         uint4 raw[4];
 #pragma unroll
@@ -121,6 +125,47 @@ column_sums_reduce_kernel(const float *__restrict__ partial, int blocks, int col
     float s = 0.f;
     for (int b = 0; b < blocks; ++b) s += partial[(int64_t)b * cols + c];
     out[c] = s;
+}
+
+// out = bfloat16(dropout mask * in) for a float32 matrix [rows, cols] (element id = r * cols + c; no mask when rng_state is
+// null) together with the column sums of what was written: the step "gradient through a residual dropout, then the bias
+// gradient of the projection under it" in one pass over the gradient instead of three.
+__global__ void __launch_bounds__(256)
+dropout_cast_colsum_kernel(const float *__restrict__ in, int64_t in_rs, __nv_bfloat16 *__restrict__ out, int64_t out_rs, int64_t rows,
+                           int cols, const unsigned long long *__restrict__ rng_state, unsigned int site0, unsigned int site1,
+                           unsigned int threshold, float scale, float *__restrict__ partial) {
+    const int rpb = cs_rows_per_block(cols);
+    const int64_t r0 = (int64_t)blockIdx.y * rpb;
+    const int rows_here = (int)((rows - r0) < rpb ? (rows - r0) : rpb);
+    const bool drop = rng_state != nullptr;
+    const unsigned long long key = drop ? *rng_state : 0ull;
+    const uint32_t salt0 = dropout_salt(key, site0, 0), salt1 = dropout_salt(key, site1, 0);
+    colsum_block(rows_here, cols, blockIdx.x * 512, partial + (int64_t)blockIdx.y * cols, [&](int r, int n, int col, float (&v)[4][8]) {
+        float4 lo[4], hi[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (u < n) {
+                const float *src = in + (r0 + r + 4 * u) * in_rs + col;
+                lo[u] = __ldg(reinterpret_cast<const float4 *>(src));
+                hi[u] = __ldg(reinterpret_cast<const float4 *>(src + 4));
+            }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (u < n) {
+                const int64_t row = r0 + r + 4 * u;
+                float w[8] = {lo[u].x, lo[u].y, lo[u].z, lo[u].w, hi[u].x, hi[u].y, hi[u].z, hi[u].w};
+                if (drop) dropout_run(w, salt0, salt1, site1 != 0, (unsigned long long)row * (unsigned long long)cols + (unsigned long long)col, threshold, scale);
+                uint4 o;
+                __nv_bfloat162 *p2 = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    p2[i] = __floats2bfloat162_rn(w[2 * i], w[2 * i + 1]);
+                    v[u][2 * i] = __low2float(p2[i]);              // the sums are those of the stored (rounded) values
+                    v[u][2 * i + 1] = __high2float(p2[i]);
+                }
+                *reinterpret_cast<uint4 *>(out + row * out_rs + col) = o;
+            }
+    });
 }
 
 // Backward of the label-smoothed cross entropy IN PLACE (the logits become their gradient) together with the column
@@ -184,19 +229,40 @@ using namespace hsa;
 
 extern "C" size_t hsa_column_sums_partial_bytes(long long rows, int cols) {
     if (rows < 1 || cols < 1) return 0;
-    return (size_t)((rows + kCsRows - 1) / kCsRows) * cols * sizeof(float);
+    const int rpb = cs_rows_per_block(cols);
+    return (size_t)((rows + rpb - 1) / rpb) * cols * sizeof(float);
 }
 
 extern "C" int hsa_column_sums(const void *x, long long row_stride, long long rows, int cols, float *out, float *partial, void *stream) {
     HSA_CHECK_ARG(x && out && partial, "hsa_column_sums: null pointer");
     HSA_CHECK_ARG(rows >= 1 && cols >= 8 && cols % 8 == 0 && row_stride % 8 == 0 && aligned16(x), "hsa_column_sums: bad shape or alignment");
-    const int blocks = (int)((rows + kCsRows - 1) / kCsRows);
+    const int rpb = cs_rows_per_block(cols);
+    const int blocks = (int)((rows + rpb - 1) / rpb);
     HSA_CHECK_ARG(blocks <= 65535, "hsa_column_sums: too many rows");
     dim3 grid((unsigned)((cols + 511) / 512), (unsigned)blocks);
     column_sums_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)x, row_stride, rows, cols, partial);
     if (int rc = launch_status("hsa_column_sums")) return rc;
     column_sums_reduce_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, (cudaStream_t)stream>>>(partial, blocks, cols, out);
     return launch_status("hsa_column_sums(reduce)");
+}
+
+extern "C" int hsa_dropout_cast_colsum(const float *in, long long in_row_stride, void *out, long long out_row_stride, long long rows,
+                                       int cols, const unsigned long long *rng_state, unsigned int site0, unsigned int site1,
+                                       unsigned int threshold, float scale, float *col_sums, float *partial, void *stream) {
+    HSA_CHECK_ARG(in && out && col_sums && partial, "hsa_dropout_cast_colsum: null pointer");
+    HSA_CHECK_ARG(rows >= 1 && cols >= 8 && cols % 8 == 0 && in_row_stride % 4 == 0 && out_row_stride % 8 == 0 && aligned16(in) && aligned16(out),
+                  "hsa_dropout_cast_colsum: bad shape or alignment");
+    HSA_CHECK_ARG(rng_state == nullptr || (site0 != 0 && (unsigned long long)rows * (unsigned long long)cols <= kDropoutRunMaxElems),
+                  "hsa_dropout_cast_colsum: bad dropout description (site 0, or more than 2^33 elements)");
+    const int rpb = cs_rows_per_block(cols);
+    const int blocks = (int)((rows + rpb - 1) / rpb);
+    HSA_CHECK_ARG(blocks <= 65535, "hsa_dropout_cast_colsum: too many rows");
+    dim3 grid((unsigned)((cols + 511) / 512), (unsigned)blocks);
+    dropout_cast_colsum_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(in, in_row_stride, (__nv_bfloat16 *)out, out_row_stride, rows, cols,
+                                                                      rng_state, site0, site1, threshold, scale, partial);
+    if (int rc = launch_status("hsa_dropout_cast_colsum")) return rc;
+    column_sums_reduce_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, (cudaStream_t)stream>>>(partial, blocks, cols, col_sums);
+    return launch_status("hsa_dropout_cast_colsum(reduce)");
 }
 
 extern "C" int hsa_cross_entropy_bwd_inplace(void *logits, long long row_stride, const long long *targets, const float *lse,

@@ -29,7 +29,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from . import _lib
-from .ops.gemm import DropoutSpec, column_sums, gemm
+from .ops.gemm import DropoutSpec, column_sums, gemm, masked_cast_with_sums
 
 BF16 = torch.bfloat16
 
@@ -275,18 +275,15 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
         new = lambda *shape, dtype=BF16: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
         spec = (lambda s0, s1=0: DropoutSpec(rng_key, p, s0, s1)) if p > 0.0 else (lambda s0, s1=0: None)
 
-        def masked_bf16(src, site, N_cols, rows_total):
-            """bfloat16 of (dropout mask of `site`) * src, src float32 [B, rows, N_cols]."""
-            if p > 0.0:
-                return spec(site).apply(src, new(*src.shape), 0, N_cols, N_cols, rows_total)
-            return src.to(BF16)
+        def masked_bf16(src, site):
+            """bfloat16 of (dropout mask of `site`) * src, src float32 [B, rows, cols], and its column sums."""
+            return masked_cast_with_sums(src, spec(site))
 
         dx2 = dx2.contiguous() if dx2.dtype == f32 else dx2.float().contiguous()
         dy_next = dy_next.contiguous() if dy_next.dtype == f32 else dy_next.float().contiguous()
         with torch.cuda.device(dev):
             # ---------------- feed-forward
-            dz2 = masked_bf16(dx2, S_FFN_OUT, d, N)
-            dbf2 = _rowsum(dz2)
+            dz2, dbf2 = masked_bf16(dx2, S_FFN_OUT)
             dW2 = gemm(dz2, h, a_t=True, b_t=True, out_dtype=f32)
             keep = 1.0 / (1.0 - p) if p > 0.0 else 1.0
             dz1 = gemm(dz2, W2b, b_t=True, gate=h, gate_scale=keep)              # through dropout and relu in one step
@@ -296,8 +293,7 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
             dx1, dg2, db2n = _ln_bwd(x1, dx1n, g2, mean2, rstd2, dx2)
 
             # ---------------- top-down
-            dzo = masked_bf16(dx1, S_ATTN, d, N)
-            dbo_x = _rowsum(dzo)
+            dzo, dbo_x = masked_bf16(dx1, S_ATTN)
             dWo_x = gemm(dzo, attn, a_t=True, b_t=True, out_dtype=f32)
             dattn = gemm(dzo, Wo_xb, b_t=True)
             G = new(B, 2 * N - 1, 3 * d)                                         # [dQ | dK | dV] (dQ: first N rows only)
@@ -313,8 +309,7 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
             gemm(G[:, N:, d:], Wkv_x, b_t=True, out=dyn_total, residual=dy_next)
 
             # ---------------- bottom-up
-            dzy = masked_bf16(dyn_total, S_YDELTA, d, M)
-            dbo_y = _rowsum(dzy)
+            dzy, dbo_y = masked_bf16(dyn_total, S_YDELTA)
             dWo_y = gemm(dzy, Rb, a_t=True, b_t=True, out_dtype=f32)
             dRf = new(B, M, d, dtype=f32)
             dRb = new(B, M, d)

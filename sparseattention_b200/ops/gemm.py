@@ -181,6 +181,28 @@ def column_sums(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def masked_cast_with_sums(src: torch.Tensor, dropout: Optional[DropoutSpec]) -> tuple:
+    """(bfloat16(mask * src), float32 column sums of it) for a contiguous float32 tensor [..., cols] in one pass: a
+    gradient on its way back through a dropout that ran in a product's epilogue (the mask is that of the logical tensor
+    `src` itself), and the bias gradient of the projection under it.  dropout=None: a plain cast with its column sums."""
+    lib = _lib.load()
+    cols = src.size(-1)
+    assert src.dtype == torch.float32 and src.is_contiguous() and cols % 8 == 0 and src.data_ptr() % 16 == 0
+    rows = src.numel() // cols
+    out = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
+    sums = torch.empty(cols, dtype=torch.float32, device=src.device)
+    partial = torch.empty(int(lib.hsa_column_sums_partial_bytes(rows, cols)) // 4, dtype=torch.float32, device=src.device)
+    if dropout is None:
+        key, s0, s1, thr, scale = None, 0, 0, 0, 1.0
+    else:
+        key, s0, s1, thr, scale = c_void_p(dropout.key.data_ptr()), dropout.site0, dropout.site1, dropout.threshold, dropout.scale
+    with torch.cuda.device(src.device):
+        rc = lib.hsa_dropout_cast_colsum(c_void_p(src.data_ptr()), cols, c_void_p(out.data_ptr()), cols, rows, cols, key, s0, s1, thr,
+                                         scale, c_void_p(sums.data_ptr()), c_void_p(partial.data_ptr()), _lib.stream_ptr(src.device))
+    _lib.check(rc, "hsa_dropout_cast_colsum")
+    return out, sums
+
+
 def gemm_aborts() -> int:
     """Thread blocks of hsa_gemm that gave up a bounded wait (0 in a healthy run); synchronises."""
     import ctypes

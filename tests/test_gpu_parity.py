@@ -361,6 +361,30 @@ def test_column_sums(hsa, shape):
     assert torch.equal(got, column_sums(x.cuda()))               # fixed summation order
 
 
+@pytest.mark.parametrize("shape", [(5, 8), (2, 333, 512), (8, 4095, 512), (1000, 2048)])
+@pytest.mark.parametrize("sites", [None, (3, 0), (4, 9)])
+def test_masked_cast_with_column_sums(hsa, shape, sites):
+    """One pass = dropout mask (that of DropoutSpec.apply on the same logical tensor) * float32 -> bfloat16, plus the column
+    sums of what was written."""
+    from sparseattention_b200.ops.gemm import DropoutSpec, column_sums, masked_cast_with_sums
+    gen = torch.Generator().manual_seed(shape[-1] + len(shape))
+    x = torch.randn(*shape, generator=gen).cuda()
+    key = torch.tensor([987654321], dtype=torch.int64, device="cuda")
+    spec = None if sites is None else DropoutSpec(key, 0.1, *sites)
+    got, sums = masked_cast_with_sums(x, spec)
+    x3 = x.reshape(1, -1, shape[-1])
+    if spec is None:
+        want = x.bfloat16()
+    else:
+        want = spec.apply(x3, torch.empty_like(x3, dtype=torch.bfloat16), 0, shape[-1], shape[-1], x3.size(1)).reshape(shape)
+    assert torch.equal(got, want)
+    want_sums = got.double().reshape(-1, shape[-1]).sum(dim=0)
+    assert rel_err(sums.cpu(), want_sums.cpu()) < 1e-5
+    if spec is not None and got.numel() >= 100000:
+        dropped = float((got == 0).float().mean())
+        assert abs(dropped - (0.1 if sites[1] == 0 else 0.19)) < 0.01
+
+
 def _gemm_inputs(batches, rows, N, K, seed):
     gen = torch.Generator().manual_seed(seed)
     A = torch.randn(batches, rows, K, generator=gen).bfloat16()
