@@ -191,5 +191,25 @@ def as_rows(t: torch.Tensor) -> torch.Tensor:
     return t if inner_contiguous(t) else t.contiguous()
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def on_device(dev: torch.device):
+    """Context that makes `dev` the current CUDA device for the calls inside it; free when it already is (the device
+    switch of torch.cuda.device costs several microseconds per call, more than a small kernel runs)."""
+    idx = dev.index
+    if idx is None or torch.cuda.current_device() == idx:
+        return _NO_SWITCH
+    return torch.cuda.device(idx)
+
+
 def stream_ptr(dev: torch.device) -> c_void_p:
     return c_void_p(torch.cuda.current_stream(dev).cuda_stream)

@@ -1,5 +1,5 @@
 // Span attention forward, tensor cores, 128-leaf tiles: the variant for the common causal case
-// (radius <= 16, bf16 / f16, head dim 64 or 128, N >= 128).
+// (radius <= 32, bf16 / f16, head dim 64 or 128, N >= 128).
 //
 // Same algorithm as span_attn_fwd_tc.cu, but a CTA covers 128 leaves with 8 warps and its K/V rows are
 // brought in by TMA (cp.async.bulk.tensor through tensor maps, completion on an mbarrier) instead of
@@ -24,7 +24,9 @@ struct SpanTc128Args {
     float *lse;
     int64_t q_bs, q_rs, k_bs, k_rs, v_bs, v_rs, o_bs, o_rs;
     int N, L, H, R;
-    int RB;          // ceil(R / 16): 0 or 1
+    int RB;          // ceil(R / 16): 0, 1 or 2
+    int split_v;     // the second 128-byte half of the V rows is loaded over the first K plane once the scores are done
+                     // (256-byte rows with a 32-leaf halo: four planes of two resident CTAs would not fit the SM)
     int band_rows;   // 128 + 16 * RB
     int kv_rows;     // band + 63 in-tile tree rows + (L - 7) upper rows
     int plane_bytes; // one [rows][128 B] plane (rows padded to a multiple of 8)
@@ -80,7 +82,10 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
     unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *Ks = smem;                                        // [NH][rows][128 B]
     unsigned char *Vs = Ks + (size_t)NH * a.plane_bytes;
-    unsigned long long *mbar = reinterpret_cast<unsigned long long *>(Vs + (size_t)NH * a.plane_bytes);
+    const bool split = NH == 2 && a.split_v != 0;
+    // where half hf of the V rows lives: its own plane, or (split) the first K plane for the second half
+    auto v_plane = [&](int hf) -> unsigned char * { return hf == 0 ? Vs : (split ? Ks : Vs + a.plane_bytes); };
+    unsigned long long *mbar = reinterpret_cast<unsigned long long *>(Vs + (size_t)(split ? 1 : NH) * a.plane_bytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ntiles = a.N / kT128;
@@ -98,21 +103,21 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
     // Thread 0 announces the bytes of all boxes; threads 0 .. 2*NH*L-1 issue one box each.  Rows nobody may
     // attend to are loaded all the same (upper levels on the causal side) or zero-filled by the copy engine
     // (before the first leaf), so masked scores and 0 * V products stay finite.
-    const uint32_t mbK = smem_u32(&mbar[0]), mbV = smem_u32(&mbar[1]);
+    const uint32_t mbK = smem_u32(&mbar[0]), mbV = smem_u32(&mbar[1]), mbV2 = smem_u32(&mbar[2]);
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbK), "r"(1) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbV), "r"(1) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbV2), "r"(1) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
     if (tid == 0) {
         const uint32_t bytes = (uint32_t)a.kv_rows * 128u * NH;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbK), "r"(bytes + a.extra_tx) : "memory");
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV), "r"(bytes) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV), "r"(split ? bytes / 2 : bytes) : "memory");
     }
-    if (tid < 2 * NH * L) {
-        const int isv = tid / (NH * L), rem = tid % (NH * L);       // K boxes first
-        const int hf = rem / L, j = rem % L;
+    // one box: tensor isv (0 = K, 1 = V), half hf, piece j of the tile's working set, onto barrier mb
+    auto issue_box = [&](int isv, int hf, int j, uint32_t mb) {
         const SpanTc128Maps &maps = isv ? vmaps : kmaps;
         const CUtensorMap *map;
         int row, dst_row;
@@ -125,9 +130,14 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
         } else {                                                   // the sibling of the tile's ancestor at level j
             map = &maps.one; row = level_base(N, j) + ((t0 >> j) ^ 1); dst_row = a.band_rows + kT128In + (j - kT128Log);
         }
-        const uint32_t dst = smem_u32((isv ? Vs : Ks) + (size_t)hf * a.plane_bytes + (size_t)dst_row * 128);
+        const uint32_t dst = smem_u32((isv ? v_plane(hf) : Ks + (size_t)hf * a.plane_bytes) + (size_t)dst_row * 128);
         asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
-                     ::"r"(dst), "l"(map), "r"(64 * hf), "r"(h), "r"(row), "r"(b), "r"(isv ? mbV : mbK) : "memory");
+                     ::"r"(dst), "l"(map), "r"(64 * hf), "r"(h), "r"(row), "r"(b), "r"(mb) : "memory");
+    };
+    if (tid < 2 * NH * L) {
+        const int isv = tid / (NH * L), rem = tid % (NH * L);       // K boxes first
+        const int hf = rem / L, j = rem % L;
+        if (!(split && isv && hf == 1)) issue_box(isv, hf, j, isv ? mbV : mbK);      // (split: that half comes later)
     }
 
     // ---------------------------------------------------------------- Q: global -> A-operand registers
@@ -145,7 +155,7 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
         }
     }
 
-    const int nbb = RB + 1;                 // band blocks: [the warp's own 16 leaves] (+ the 16 before them)
+    const int nbb = RB + 1;                 // band blocks: the warp's own 16 leaves, then the RB blocks of 16 before them
     const int ntb = (L + 3 + 15) >> 4;      // tree blocks: 7 slots of levels 1..3 + one slot per level 4..L-1
     const int nblk = nbb + ntb;             // <= NB (checked by the launcher)
 
@@ -169,9 +179,10 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
     const int dbase = 2 * quad - qrow;
     const bool odd = qrow & 1;              // odd leaves see their level-0 sibling (the leaf before them)
 
-    // shared-memory row of key kk (0..15) of block o: 0 = own leaves, 1 = the 16 leaves before (when RB = 1), then tree blocks
+    // shared-memory row of key kk (0..15) of block o: 0 = own leaves, 1 .. RB = the blocks of 16 leaves before them (nearest
+    // first), then tree blocks
     auto key_row = [&](int o, int kk) -> int {
-        if (o < nbb) return lw + 16 * (o == 0 ? RB : 0) + kk;
+        if (o < nbb) return lw + 16 * (RB - o) + kk;
         int row, jj;
         tree_slot128(16 * (o - nbb) + kk, warp, L, row, jj);
         return a.band_rows + row;
@@ -214,11 +225,22 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
             }
         }
     }
+    if (split) {
+        // K is dead: the second half of the V rows may land on its first plane.  The reads above went through the generic
+        // proxy, the copies write through the async proxy.
+        __syncthreads();
+        if (tid == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbV2), "r"((uint32_t)a.kv_rows * 128u) : "memory");
+        if (tid < L) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            issue_box(1, 1, tid, mbV2);
+        }
+    }
     // ---- masks and base-2 logits
 #pragma unroll
     for (int bi = 0; bi < NB; ++bi) {
         if (bi < nbb) {
-            const int blk = (bi == 0) ? RB : 0;                   // band block index, 0 = leftmost
+            const int blk = RB - bi;                              // band block index, 0 = leftmost
             const int r0 = t0 + lw + 16 * (blk - RB);
             const bool self = bi == 0;
             const int d0 = dbase + 16 * (blk - RB);
@@ -288,27 +310,39 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
         pa[bi][3] = pack2<T>(s[bi][1][2] * i1, s[bi][1][3] * i1);
     }
 
-    if (!__syncthreads_and(mbar_wait_phase0(mbV, a.wait_limit))) {        // V has landed
+    if (!__syncthreads_and(mbar_wait_phase0(mbV, a.wait_limit))) {        // V has landed (split: its first half)
+        if (split) mbar_wait_phase0(mbV2, a.wait_limit);
         give_up();
         return;
     }
 
-    // ---------------------------------------------------------------- O = P V
+    // ---------------------------------------------------------------- O = P V, one 128-byte half of the head dim at a time
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 #pragma unroll
-    for (int bi = 0; bi < NB; ++bi) {
-        if (bi < nblk) {
-            const int vrow = key_row(bi, (lane & 7) + 8 * ((lane >> 3) & 1));
-            const uint32_t vb = smem_u32(Vs + (size_t)vrow * 128);
-            const int vsw = ((lane >> 4) ^ vrow) & 7;
+    for (int hf = 0; hf < NH; ++hf) {
+        if (hf == 1 && split) {
+            if (!__syncthreads_and(mbar_wait_phase0(mbV2, a.wait_limit))) {   // the second half has landed
+                give_up();
+                return;
+            }
+        }
+        const unsigned char *Vp = v_plane(hf);
 #pragma unroll
-            for (int dp = 0; dp < D / 16; ++dp) {
-                uint32_t vf[4];
-                ldmatrix_x4_trans(vf, vb + (dp >> 2) * a.plane_bytes + (((2 * dp) & 7) ^ vsw) * 16);
-                mma16816<T>(o[2 * dp], pa[bi], vf[0], vf[1]);
-                mma16816<T>(o[2 * dp + 1], pa[bi], vf[2], vf[3]);
+        for (int bi = 0; bi < NB; ++bi) {
+            if (bi < nblk) {
+                const int vrow = key_row(bi, (lane & 7) + 8 * ((lane >> 3) & 1));
+                const uint32_t vb = smem_u32(Vp + (size_t)vrow * 128);
+                const int vsw = ((lane >> 4) ^ vrow) & 7;
+#pragma unroll
+                for (int dq = 0; dq < 4; ++dq) {
+                    const int dp = 4 * hf + dq;
+                    uint32_t vf[4];
+                    ldmatrix_x4_trans(vf, vb + (((2 * dq) & 7) ^ vsw) * 16);
+                    mma16816<T>(o[2 * dp], pa[bi], vf[0], vf[1]);
+                    mma16816<T>(o[2 * dp + 1], pa[bi], vf[2], vf[3]);
+                }
             }
         }
     }
@@ -359,7 +393,7 @@ bool hsa_span_attn_fwd_tc128_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_v
     if (N < kT128 || (N & (N - 1)) != 0) return false;
     const int L = ilog2((unsigned)N);
     if (L + 3 > 32) return false;                        // the warp's tree keys must fit two 16-key blocks
-    if (radius < 0 || radius > 16) return false;
+    if (radius < 0 || radius > 32) return false;
     if (((radius + 15) / 16 + 1) + ((L + 3 + 15) / 16) > 4) return false;
     if (B < 1 || H < 1) return false;
     if ((int64_t)(N / kT128) * H * B > 0x7fffffffLL) return false;
@@ -402,7 +436,8 @@ static bool tensor_maps(const hsa_view &v, int B, int N, int H, int D, int band_
 
 template <typename T, int D>
 static int launch_tc128(const SpanTc128Args &a, const SpanTc128Maps &km, const SpanTc128Maps &vm, int B, cudaStream_t st) {
-    const size_t smem = (size_t)2 * (D / 64) * a.plane_bytes + 16 + 1024;     // planes, two mbarriers, alignment slack
+    const int planes = a.split_v ? 3 : 2 * (D / 64);
+    const size_t smem = (size_t)planes * a.plane_bytes + 32 + 1024;           // planes, three mbarriers, alignment slack
     const int64_t total = (int64_t)B * (a.N / kT128) * a.H;
     const int nblk = (a.RB + 1) + ((a.L + 3 + 15) >> 4);
     auto go = [&](auto kernel) -> int {
@@ -427,6 +462,8 @@ int hsa_span_attn_fwd_tc128(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, fl
     a.band_rows = kT128 + 16 * a.RB;
     a.kv_rows = a.band_rows + kT128In + (a.L - kT128Log);
     a.plane_bytes = (a.kv_rows + 7) / 8 * 8 * 128;
+    // four planes per CTA of 256-byte rows stop fitting twice into an SM's shared memory once the halo is 32 leaves
+    a.split_v = (D == 128 && 2 * (4 * (size_t)a.plane_bytes + 2048) > 227 * 1024) ? 1 : 0;
     a.scale_log2e = 1.4426950408889634f / sqrtf((float)D);
     a.wait_limit = wait_limit_cycles();
     a.extra_tx = wait_extra_tx();

@@ -201,7 +201,7 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
         sizes, offs = level_layout(N)
         drop = (lambda s0, s1=0: DropoutSpec(rng_key, p, s0, s1)) if p > 0.0 else (lambda s0, s1=0: None)
         new = lambda *shape, dtype=BF16: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             # row-stacked bfloat16 weights: one product per shared input
             Wqkv_y = torch.cat([Wq_y, Wk_y, Wv_y], dim=0).to(BF16)
             Wkv_y = Wqkv_y[d:]
@@ -281,7 +281,7 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
 
         dx2 = dx2.contiguous() if dx2.dtype == f32 else dx2.float().contiguous()
         dy_next = dy_next.contiguous() if dy_next.dtype == f32 else dy_next.float().contiguous()
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             # ---------------- feed-forward
             dz2, dbf2 = masked_bf16(dx2, S_FFN_OUT)
             dW2 = gemm(dz2, h, a_t=True, b_t=True, out_dtype=f32)

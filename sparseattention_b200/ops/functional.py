@@ -36,7 +36,7 @@ class BuildParentNodesFunc(torch.autograd.Function):
         dt = _lib.dtype_code(Q_p)
         assert all(t.dtype == Q_p.dtype for t in (K_p, V_p, K_c, V_c)), "dtype mismatch"
         Out = torch.empty((B, P, H, D), dtype=Q_p.dtype, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_parent_nodes_fwd(*(_lib.rows_view(t) for t in (Q_p, K_p, V_p, K_c, V_c, Out)),
                                           None, B, P, H, D, dt, _lib.stream_ptr(dev))
         _lib.check(rc, "hsa_parent_nodes_fwd")
@@ -52,7 +52,7 @@ class BuildParentNodesFunc(torch.autograd.Function):
         grad_output = _lib.as_rows(grad_output)
         dQ, dKp, dVp = (torch.empty((B, P, H, D), dtype=Q_p.dtype, device=dev) for _ in range(3))
         dKc, dVc = (torch.empty((B, 2 * P, H, D), dtype=Q_p.dtype, device=dev) for _ in range(2))
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_parent_nodes_bwd(
                 *(_lib.rows_view(t) for t in (grad_output, Q_p, K_p, V_p, K_c, V_c, dQ, dKp, dVp, dKc, dVc)),
                 B, P, H, D, _lib.dtype_code(Q_p), _lib.stream_ptr(dev))
@@ -120,7 +120,7 @@ def span_attention_forward(Q, K, V, window_size: int, is_causal: bool, need_lse:
     assert K.dtype == Q.dtype and V.dtype == Q.dtype, "dtype mismatch"
     Out = torch.empty((B, N, H, D), dtype=Q.dtype, device=dev)
     LSE = torch.empty((B, N, H), dtype=torch.float32, device=dev) if need_lse else None
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.hsa_span_attn_fwd(*(_lib.rows_view(t) for t in (Q, K, V, Out)),
                                    c_void_p(LSE.data_ptr()) if need_lse else None,
                                    B, N, H, D, int(window_size), int(is_causal), _lib.dtype_code(Q), algo,
@@ -143,7 +143,7 @@ def span_attention_backward(Q, K, V, Out, LSE, dOut, window_size: int, is_causal
     dt = _lib.dtype_code(Q)
     nbytes = int(lib.hsa_span_attn_bwd_workspace_bytes(B, N, H, D, int(window_size), int(is_causal), dt, algo))
     ws = torch.empty((max(nbytes, 256) + 255) // 256 * 256, dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.hsa_span_attn_bwd(
             *(_lib.rows_view(t) for t in (Q, K, V, Out)), c_void_p(LSE.data_ptr()),
             *(_lib.rows_view(t) for t in (dOut, dQ, dK, dV)), c_void_p(ws.data_ptr()), ws.numel(),
@@ -165,7 +165,7 @@ def span_attention_logits(Q, K, window_size: int, is_causal: bool, weights: bool
     assert K.shape == (B, 2 * N - 1, H, D) and K.dtype == Q.dtype, "K must be [B, 2N-1, H, D] of Q's dtype"
     L = int(math.log2(N)) if N > 1 else 0
     out = torch.empty((B, N, H, 2 * int(window_size) + 1 + L), dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.hsa_span_attn_logits(_lib.rows_view(Q), _lib.rows_view(K), c_void_p(out.data_ptr()), B, N, H, D,
                                       int(window_size), int(is_causal), int(weights), _lib.dtype_code(Q),
                                       _lib.stream_ptr(dev))
@@ -186,7 +186,7 @@ def build_hierarchical_logits(ALL_Q, ALL_K, H: int, D: int, seq_len: int):
     k = ALL_K.contiguous().view(B, total, H, D)
     res_self = torch.empty((B, seq_len, H), dtype=torch.float32, device=dev)
     res_cross = torch.empty((B, total - 1, H), dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.hsa_sibling_logits(_lib.rows_view(q), _lib.rows_view(k), c_void_p(res_self.data_ptr()),
                                     c_void_p(res_cross.data_ptr()), B, total, int(seq_len), H, D, _lib.dtype_code(q),
                                     _lib.stream_ptr(dev))
@@ -205,7 +205,7 @@ def span_attention_decode(q, K, V, n: int, window_size: int):
     q4 = q.reshape(B, 1, H, D).contiguous()
     K, V = _lib.as_rows(K), _lib.as_rows(V)
     out = torch.empty_like(q4)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.hsa_span_attn_decode(_lib.rows_view(q4), _lib.rows_view(K), _lib.rows_view(V), _lib.rows_view(out),
                                       B, N, H, D, int(window_size), int(n), _lib.dtype_code(q4), _lib.stream_ptr(dev))
     _lib.check(rc, "hsa_span_attn_decode")

@@ -47,7 +47,7 @@ class DropoutSpec:
         of columns col_begin+col_shift.. of the logical [batches, rows_total, N] tensor, rows row_offset.. ."""
         lib = _lib.load()
         dev = src.device
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_dropout_apply(_lib.rows_view(src), _lib.dtype_code(src), _lib.rows_view(out), src.size(0), src.size(1),
                                        int(col_begin), int(ncols), int(N), int(rows_total), int(row_offset), int(col_shift),
                                        c_void_p(self.key.data_ptr()), self.site0, self.site1, self.threshold, self.scale,
@@ -154,7 +154,7 @@ def gemm(A: torch.Tensor, B: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     ws = torch.empty(need + 256, dtype=torch.uint8, device=dev) if need else None
     ws_ptr = ((ws.data_ptr() + 255) // 256 * 256) if need else 0
     import ctypes
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.hsa_gemm_ex(_lib.rows_view(A3), _lib.rows_view(B3), _lib.rows_view(out3),
                              c_void_p(bias32.data_ptr()) if bias32 is not None else None,
                              batches, rows, N, K, int(a_t), int(b_t), _lib.dtype_code(out), int(accumulate), int(splits),
@@ -174,7 +174,7 @@ def column_sums(x: torch.Tensor) -> torch.Tensor:
     rows = x2.size(0)
     out = torch.empty(cols, dtype=torch.float32, device=x.device)
     partial = torch.empty(int(lib.hsa_column_sums_partial_bytes(rows, cols)) // 4, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         rc = lib.hsa_column_sums(c_void_p(x2.data_ptr()), x2.stride(0), rows, cols, c_void_p(out.data_ptr()),
                                  c_void_p(partial.data_ptr()), _lib.stream_ptr(x.device))
     _lib.check(rc, "hsa_column_sums")
@@ -196,7 +196,7 @@ def masked_cast_with_sums(src: torch.Tensor, dropout: Optional[DropoutSpec]) -> 
         key, s0, s1, thr, scale = None, 0, 0, 0, 1.0
     else:
         key, s0, s1, thr, scale = c_void_p(dropout.key.data_ptr()), dropout.site0, dropout.site1, dropout.threshold, dropout.scale
-    with torch.cuda.device(src.device):
+    with _lib.on_device(src.device):
         rc = lib.hsa_dropout_cast_colsum(c_void_p(src.data_ptr()), cols, c_void_p(out.data_ptr()), cols, rows, cols, key, s0, s1, thr,
                                          scale, c_void_p(sums.data_ptr()), c_void_p(partial.data_ptr()), _lib.stream_ptr(src.device))
     _lib.check(rc, "hsa_dropout_cast_colsum")

@@ -34,7 +34,7 @@ class _CrossEntropy(torch.autograd.Function):
         assert 1 <= V <= Vp
         loss_rows = torch.empty(M, dtype=torch.float32, device=dev)
         lse = torch.empty(M, dtype=torch.float32, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_cross_entropy_fwd(c_void_p(logits.data_ptr()), logits.stride(0), c_void_p(targets.data_ptr()),
                                            c_void_p(loss_rows.data_ptr()), c_void_p(lse.data_ptr()), M, V,
                                            float(label_smoothing), int(ignore_index), _lib.dtype_code(logits),
@@ -54,7 +54,7 @@ class _CrossEntropy(torch.autograd.Function):
         M, Vp = logits.shape
         scale = (grad_out.to(torch.float32) / count).reshape(1).contiguous()
         dlogits = torch.empty_like(logits)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_cross_entropy_bwd(c_void_p(logits.data_ptr()), logits.stride(0), c_void_p(targets.data_ptr()),
                                            c_void_p(lse.data_ptr()), c_void_p(scale.data_ptr()),
                                            c_void_p(dlogits.data_ptr()), dlogits.stride(0), M, V, Vp, eps, ignore,
@@ -90,7 +90,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
         gemm(xb, wb, bias=bias, out=logits, ce_partial=partial, ce_targets=targets, ce_classes=V, ce_skip_store=not need_grad)
         loss_rows = torch.empty(M, dtype=torch.float32, device=dev)
         lse = torch.empty(M, dtype=torch.float32, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_linear_ce_combine(c_void_p(partial.data_ptr()), M, Vp, c_void_p(targets.data_ptr()),
                                            c_void_p(loss_rows.data_ptr()), c_void_p(lse.data_ptr()), V, float(label_smoothing),
                                            int(ignore_index), _lib.stream_ptr(dev))
@@ -112,7 +112,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
         scale = (grad_out.to(torch.float32) / count).reshape(1).contiguous()
         col_sums = torch.empty(Vp, dtype=torch.float32, device=dev)
         partial = torch.empty(int(lib.hsa_column_sums_partial_bytes(M, Vp)) // 4, dtype=torch.float32, device=dev)
-        with torch.cuda.device(dev):          # the gradient overwrites the logits in place; its column sums are the bias gradient
+        with _lib.on_device(dev):          # the gradient overwrites the logits in place; its column sums are the bias gradient
             rc = lib.hsa_cross_entropy_bwd_inplace(c_void_p(logits.data_ptr()), logits.stride(0), c_void_p(targets.data_ptr()),
                                                    c_void_p(lse.data_ptr()), c_void_p(scale.data_ptr()), M, V, Vp, eps, ignore,
                                                    c_void_p(col_sums.data_ptr()), c_void_p(partial.data_ptr()), _lib.stream_ptr(dev))

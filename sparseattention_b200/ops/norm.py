@@ -28,7 +28,7 @@ class _LayerNorm(torch.autograd.Function):
         y = torch.empty_like(xc)
         mean = torch.empty(rows, dtype=torch.float32, device=dev)
         rstd = torch.empty(rows, dtype=torch.float32, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_layer_norm_fwd(c_void_p(xc.data_ptr()), c_void_p(w32.data_ptr()), c_void_p(b32.data_ptr()),
                                         c_void_p(y.data_ptr()), c_void_p(mean.data_ptr()), c_void_p(rstd.data_ptr()),
                                         rows, d, float(eps), _lib.dtype_code(xc), _lib.stream_ptr(dev))
@@ -52,7 +52,7 @@ class _LayerNorm(torch.autograd.Function):
         dbeta = torch.empty(d, dtype=torch.float32, device=dev)
         ctas = int(lib.hsa_layer_norm_bwd_ctas(rows))
         partial = torch.empty(ctas * 2 * d, dtype=torch.float32, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_layer_norm_bwd(c_void_p(xc.data_ptr()), c_void_p(dy.data_ptr()), c_void_p(w32.data_ptr()),
                                         c_void_p(mean.data_ptr()), c_void_p(rstd.data_ptr()), c_void_p(dx.data_ptr()),
                                         c_void_p(dgamma.data_ptr()), c_void_p(dbeta.data_ptr()),

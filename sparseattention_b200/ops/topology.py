@@ -29,7 +29,7 @@ def build_tree_topology(seq_len: int, is_causal: bool = True, device="cuda", dty
     if run_dev.index is None:
         run_dev = torch.device("cuda", torch.cuda.current_device())
     L = int(math.log2(seq_len))
-    with torch.cuda.device(run_dev):
+    with _lib.on_device(run_dev):
         idx = torch.empty((seq_len, L), dtype=torch.int32, device=run_dev)
         mask = torch.empty((seq_len, L), dtype=torch.uint8, device=run_dev)
         gather = torch.empty((2 * seq_len - 1, 3), dtype=torch.int32, device=run_dev)
@@ -52,7 +52,7 @@ class _SpanInputY(torch.autograd.Function):
         B, N, D = x.shape
         M = int(lib.hsa_span_input_y_rows(N))
         y = torch.empty((B, M, D), dtype=x.dtype, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_span_input_y_fwd(_lib.rows_view(x), _lib.rows_view(y), B, N, D, _lib.dtype_code(x),
                                           _lib.stream_ptr(dev))
         _lib.check(rc, "hsa_span_input_y_fwd")
@@ -66,7 +66,7 @@ class _SpanInputY(torch.autograd.Function):
         gy = _lib.as_rows(gy)
         dev = gy.device
         gx = torch.empty((B, N, D), dtype=gy.dtype, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.hsa_span_input_y_bwd(_lib.rows_view(gy), _lib.rows_view(gx), B, N, D, _lib.dtype_code(gy),
                                           _lib.stream_ptr(dev))
         _lib.check(rc, "hsa_span_input_y_bwd")
