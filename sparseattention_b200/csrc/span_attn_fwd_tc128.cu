@@ -69,7 +69,7 @@ __device__ __forceinline__ int tree_slot128(int s, int w, int L, int &row, int &
     return l;
 }
 
-template <typename T, int D, int NB>      // NB: key blocks per warp the code is unrolled for (3 or 4)
+template <typename T, int D, int NB>      // NB: key blocks per warp the code is unrolled for (3, 4 or 5)
 __global__ void __launch_bounds__(256, 2)
 span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Maps kmaps,
                       const __grid_constant__ SpanTc128Maps vmaps) {
@@ -394,7 +394,7 @@ bool hsa_span_attn_fwd_tc128_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_v
     const int L = ilog2((unsigned)N);
     if (L + 3 > 32) return false;                        // the warp's tree keys must fit two 16-key blocks
     if (radius < 0 || radius > 32) return false;
-    if (((radius + 15) / 16 + 1) + ((L + 3 + 15) / 16) > 4) return false;
+    if (((radius + 15) / 16 + 1) + ((L + 3 + 15) / 16) > 5) return false;
     if (B < 1 || H < 1) return false;
     if ((int64_t)(N / kT128) * H * B > 0x7fffffffLL) return false;
     if (!view_vec_ok(Q, 2) || !view_vec_ok(K, 2) || !view_vec_ok(V, 2) || !view_vec_ok(Out, 2)) return false;
@@ -446,7 +446,8 @@ static int launch_tc128(const SpanTc128Args &a, const SpanTc128Maps &km, const S
         kernel<<<(unsigned)total, 256, smem, st>>>(a, km, vm);
         return launch_status("hsa_span_attn_fwd(tc128)");
     };
-    return nblk <= 3 ? go(span_fwd_tc128_kernel<T, D, 3>) : go(span_fwd_tc128_kernel<T, D, 4>);
+    if (nblk <= 3) return go(span_fwd_tc128_kernel<T, D, 3>);
+    return nblk == 4 ? go(span_fwd_tc128_kernel<T, D, 4>) : go(span_fwd_tc128_kernel<T, D, 5>);
 }
 
 int hsa_span_attn_fwd_tc128(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H, int D,

@@ -245,6 +245,15 @@ def test_span_attention_tensor_core_128_leaf_tiles(hsa, case, dtype):
     run_span_case(hsa, *case, True, dtype, algo=3)          # 64-leaf forward and the 4-warp backward
 
 
+@pytest.mark.parametrize("case", [(1, 128, 2, 128, 17), (2, 256, 3, 128, 32), (1, 1024, 2, 64, 32), (1, 4096, 2, 128, 24),
+                                  (1, 8192, 1, 128, 32), (1, 16384, 1, 128, 32), (1, 32768, 1, 64, 31)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_span_attention_128_leaf_tiles_wide_window(hsa, case, dtype):
+    """The 128-leaf-tile forward with a halo of two 16-leaf blocks (radius 17..32): 256-byte rows load the second half of
+    V over the dead K plane; beyond N = 8192 a warp scores five key blocks."""
+    run_span_case(hsa, *case, True, dtype, algo=4, check_grad=False)
+
+
 @pytest.mark.parametrize("case", [(2, 256, 12, 64, 8), (1, 1024, 12, 64, 16), (1, 2048, 12, 128, 16),
                                   (1, 4096, 16, 128, 16)])
 @pytest.mark.parametrize("algo", [0, 3])
