@@ -349,8 +349,9 @@ int hsa_copy_rows_async(void *dst, size_t dst_pitch, const void *src, size_t src
 /* LayerNorm with float32 rows in and bfloat16 rows out (the normalised activations feed bfloat16 products), and its
  * backward: bfloat16 upstream gradient, float32 input gradient dx = add + (gradient through the norm), `add` (NULL: none;
  * may equal dx) being the gradient arriving through the residual connection around the branch
- * (Hierarchical_Transformer_Pretrain.py:386,411,421). */
-int hsa_layer_norm_fwd_mixed(const float *x, const float *gamma, const float *beta, void *y_bf16, float *mean,
+ * (Hierarchical_Transformer_Pretrain.py:386,411,421).  x_bf16 (NULL: none) also receives the input rows themselves as
+ * bfloat16, for the products that read the un-normalised rows (the child projections of the leaves). */
+int hsa_layer_norm_fwd_mixed(const float *x, const float *gamma, const float *beta, void *y_bf16, void *x_bf16, float *mean,
                              float *rstd, int64_t rows, int d, float eps, void *stream);
 int hsa_layer_norm_bwd_mixed(const float *x, const void *dy_bf16, const float *gamma, const float *mean,
                              const float *rstd, const float *add, float *dx, float *dgamma, float *dbeta,

@@ -82,7 +82,7 @@ SIGNATURES = {
     "hsa_linear_ce_partial_bytes": (c_size_t, [ctypes.c_longlong, c_int]),
     "hsa_linear_ce_combine": (c_int, [c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float,
                                       ctypes.c_longlong, c_void_p]),
-    "hsa_layer_norm_fwd_mixed": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_float, c_void_p]),
+    "hsa_layer_norm_fwd_mixed": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_float, c_void_p]),
     "hsa_layer_norm_bwd_mixed": (c_int, [c_void_p] * 10 + [c_int64, c_int, c_void_p]),
     "hsa_column_sums_partial_bytes": (c_size_t, [ctypes.c_longlong, c_int]),
     "hsa_column_sums": (c_int, [c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_int, c_void_p, c_void_p, c_void_p]),

@@ -41,7 +41,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 template <typename T, int NV, typename TY = T>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layer_norm_fwd_kernel(const T *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
-                      TY *__restrict__ y, float *__restrict__ mean, float *__restrict__ rstd, int64_t rows, float eps) {
+                      TY *__restrict__ y, float *__restrict__ mean, float *__restrict__ rstd, int64_t rows, float eps,
+                      TY *__restrict__ xcopy = nullptr /* optional: the input rows themselves, converted to TY */) {
     constexpr int d = 128 * NV;
     const int lane = threadIdx.x & 31;
     const int64_t warps = (int64_t)gridDim.x * kLnWarps;
@@ -58,6 +59,10 @@ layer_norm_fwd_kernel(const T *__restrict__ x, const float *__restrict__ gamma, 
         for (int i = 0; i < NV; ++i) {
             v[i] = ln_load4<T>(x + r * d + 4 * (lane + 32 * i));
             s += v[i].x + v[i].y + v[i].z + v[i].w;
+        }
+        if (xcopy != nullptr) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) ln_store4<TY>(xcopy + r * d + 4 * (lane + 32 * i), v[i]);
         }
         const float mu = warp_sum(s) * (1.f / d);
         float q = 0.f;
@@ -235,15 +240,16 @@ extern "C" int hsa_layer_norm_bwd(const void *x, const void *dy, const float *ga
 // float32 rows in, bfloat16 rows out (the normalised activations feed bfloat16 products), and the matching backward:
 // bfloat16 upstream gradient, float32 gradient of the input, optionally ADDED to what dx already holds (the gradient
 // arriving through the residual connection around the normalised branch).
-extern "C" int hsa_layer_norm_fwd_mixed(const float *x, const float *gamma, const float *beta, void *y_bf16, float *mean,
-                                        float *rstd, int64_t rows, int d, float eps, void *stream) {
+extern "C" int hsa_layer_norm_fwd_mixed(const float *x, const float *gamma, const float *beta, void *y_bf16, void *x_bf16,
+                                        float *mean, float *rstd, int64_t rows, int d, float eps, void *stream) {
     HSA_CHECK_ARG(x && gamma && beta && y_bf16 && mean && rstd, "hsa_layer_norm_fwd_mixed: null pointer");
     HSA_CHECK_ARG(rows >= 1, "hsa_layer_norm_fwd_mixed: rows=%lld", (long long)rows);
-    HSA_CHECK_ARG(aligned16(x) && aligned16(y_bf16) && aligned16(gamma) && aligned16(beta), "hsa_layer_norm_fwd_mixed: pointers must be 16-byte aligned");
+    HSA_CHECK_ARG(aligned16(x) && aligned16(y_bf16) && aligned16(x_bf16) && aligned16(gamma) && aligned16(beta),
+                  "hsa_layer_norm_fwd_mixed: pointers must be 16-byte aligned");
     int rc = 0;
     const bool ok = ln_dispatch_width(d, [&]<int NV>() {
         layer_norm_fwd_kernel<float, NV, __nv_bfloat16><<<ln_grid(rows), kLnWarps * 32, 0, (cudaStream_t)stream>>>(
-            x, gamma, beta, (__nv_bfloat16 *)y_bf16, mean, rstd, rows, eps);
+            x, gamma, beta, (__nv_bfloat16 *)y_bf16, mean, rstd, rows, eps, (__nv_bfloat16 *)x_bf16);
         rc = launch_status("hsa_layer_norm_fwd_mixed");
     });
     if (!ok) return fail(HSA_ERR_ARG, "hsa_layer_norm_fwd_mixed: width %d not supported (128, 256, 384, 512, 768)", d);

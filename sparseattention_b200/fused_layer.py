@@ -41,18 +41,19 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else c_void_p(t.data_ptr())
 
 
-def _ln_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float):
-    """float32 [.., d] -> (bfloat16 [.., d], mean [rows], rstd [rows])."""
+def _ln_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float, raw_copy: bool = False):
+    """float32 [.., d] -> (bfloat16 [.., d], mean [rows], rstd [rows]); raw_copy: also the input itself as bfloat16."""
     lib = _lib.load()
     d = x.size(-1)
     rows = x.numel() // d
     y = torch.empty(x.shape, dtype=BF16, device=x.device)
+    xb = torch.empty(x.shape, dtype=BF16, device=x.device) if raw_copy else None
     mean = torch.empty(rows, dtype=torch.float32, device=x.device)
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-    rc = lib.hsa_layer_norm_fwd_mixed(_ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(mean), _ptr(rstd), rows, d, float(eps),
-                                      _lib.stream_ptr(x.device))
+    rc = lib.hsa_layer_norm_fwd_mixed(_ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(xb), _ptr(mean),
+                                      _ptr(rstd), rows, d, float(eps), _lib.stream_ptr(x.device))
     _lib.check(rc, "hsa_layer_norm_fwd_mixed")
-    return y, mean, rstd
+    return (y, xb, mean, rstd) if raw_copy else (y, mean, rstd)
 
 
 def _ln_bwd(x, dy, gamma, mean, rstd, add):
@@ -203,16 +204,21 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
         new = lambda *shape, dtype=BF16: torch.empty(shape, dtype=dtype, device=dev)      # noqa: E731
         with _lib.on_device(dev):
             # row-stacked bfloat16 weights: one product per shared input
-            Wqkv_y = torch.cat([Wq_y, Wk_y, Wv_y], dim=0).to(BF16)
+            w16 = cfg.get("w16")
+            if w16 is not None:                     # kept by the model, refreshed once per step for all layers
+                Wqkv_y, Wqkv_x, Wo_yb, Wo_xb, W1b, W2b = w16
+            else:
+                Wqkv_y = torch.cat([Wq_y, Wk_y, Wv_y], dim=0).to(BF16)
+                Wqkv_x = torch.cat([Wq_x, Wk_x, Wv_x], dim=0).to(BF16)
+                Wo_yb, Wo_xb, W1b, W2b = Wo_y.to(BF16), Wo_x.to(BF16), W1.to(BF16), W2.to(BF16)
             Wkv_y = Wqkv_y[d:]
-            Wqkv_x = torch.cat([Wq_x, Wk_x, Wv_x], dim=0).to(BF16)
             Wkv_x = Wqkv_x[d:]
-            Wo_yb, Wo_xb, W1b, W2b = Wo_y.to(BF16), Wo_x.to(BF16), W1.to(BF16), W2.to(BF16)
 
             # ---------------- bottom-up: refresh the parents
             yn, mean_y, rstd_y = _ln_fwd(y, gy, by, eps)
             QKVp = gemm(yn, Wqkv_y)                                             # [B, M, 3d]
-            xb = x.to(BF16)
+            # the leaves' norm is taken here already: the same pass over x leaves its bfloat16 copy for the child projection
+            xn, xb, mean1, rstd1 = _ln_fwd(x, g1, b1n, eps, raw_copy=True)
             KVc0 = gemm(xb, Wkv_y, dropout=drop(S_LEAF_A, S_LEAF_B), drop_cols=(d, 2 * d))       # leaf values dropped twice
             Rb = new(B, M, d)                                                   # refreshed parents, level after level
             KVc = new(B, M, 2 * d)                                              # child projections of levels >= 1 (row = child's row in Rb)
@@ -236,7 +242,6 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
             gemm(Rb, Wo_yb, bias=bo_y, out=y_next, dropout=drop(S_YDELTA), residual=y, copy_bf16=ynb)
 
             # ---------------- top-down: span attention on the leaves
-            xn, mean1, rstd1 = _ln_fwd(x, g1, b1n, eps)
             Q = gemm(xn, Wqkv_x[:d])
             KV = new(B, 2 * N - 1, 2 * d)
             gemm(xn, Wkv_x, out=KV[:, :N], dropout=drop(S_VALUES), drop_cols=(d, 2 * d), drop_rows_total=2 * N - 1)
@@ -356,6 +361,50 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
         return (dx, dy, None, None) + grads
 
 
+class Bf16Weights:
+    """bfloat16 copies of the weight matrices of a stack of decoder layers, row-stacked the way the fused layer multiplies
+    them ([Wq; Wk; Wv] per stream), in one flat buffer that a single multi-tensor copy refreshes: a training step then
+    converts its weights with one launch instead of nine small ones per layer."""
+
+    def __init__(self, layers):
+        self.sources, shapes = [], []
+        for layer in layers:
+            a, ff = layer.self_attn, layer.feed_forward
+            groups = ([a.Wq_y.weight, a.Wk_y.weight, a.Wv_y.weight], [a.Wq_x.weight, a.Wk_x.weight, a.Wv_x.weight],
+                      [a.out_proj_y.weight], [a.out_proj_x.weight], [ff.fc1.weight], [ff.fc2.weight])
+            self.sources.append(groups)
+            shapes.append([(sum(w.size(0) for w in g), g[0].size(1)) for g in groups])
+        dev = self.sources[0][0][0].device
+        self.flat = torch.empty(sum(r * c for sh in shapes for r, c in sh), dtype=BF16, device=dev)
+        self.per_layer, self._dst, self._src, off = [], [], [], 0
+        for groups, sh in zip(self.sources, shapes):
+            mats = []
+            for g, (r, c) in zip(groups, sh):
+                m = self.flat[off: off + r * c].view(r, c)
+                off += r * c
+                mats.append(m)
+                row = 0
+                for w in g:
+                    self._dst.append(m[row: row + w.size(0)])
+                    self._src.append(w)
+                    row += w.size(0)
+            self.per_layer.append(tuple(mats))
+
+    def matches(self, layers) -> bool:
+        if len(layers) != len(self.sources):
+            return False
+        flat_src = [w for groups in self.sources for g in groups for w in g]
+        now = [w for layer in layers for w in (layer.self_attn.Wq_y.weight, layer.self_attn.Wk_y.weight, layer.self_attn.Wv_y.weight,
+                                              layer.self_attn.Wq_x.weight, layer.self_attn.Wk_x.weight, layer.self_attn.Wv_x.weight,
+                                              layer.self_attn.out_proj_y.weight, layer.self_attn.out_proj_x.weight,
+                                              layer.feed_forward.fc1.weight, layer.feed_forward.fc2.weight)]
+        return all(a is b for a, b in zip(flat_src, now)) and now[0].device == self.flat.device
+
+    def refresh(self) -> None:
+        with torch.no_grad():
+            torch._foreach_copy_(self._dst, self._src)
+
+
 def fused_layer_parameters(layer) -> tuple:
     """The parameters of a DecoderLayer in the order FusedDecoderLayerFunction takes them."""
     a, ff = layer.self_attn, layer.feed_forward
@@ -395,6 +444,7 @@ def fused_decoder_layer(layer, x: torch.Tensor, y: torch.Tensor, mask) -> Tuple[
     """DecoderLayer.forward through the fused node (call only when fused_layer_supported(...))."""
     a = layer.self_attn
     p = float(layer.dropout.p) if layer.training else 0.0
-    cfg = {"heads": a.num_heads, "window": int(a.window_size), "causal": mask is not None, "p": p, "eps": float(layer.norm1.eps)}
+    cfg = {"heads": a.num_heads, "window": int(a.window_size), "causal": mask is not None, "p": p, "eps": float(layer.norm1.eps),
+           "w16": getattr(layer, "_w16", None)}
     key = next_rng_key(x.device) if p > 0.0 else torch.zeros(1, dtype=torch.int64, device=x.device)
     return FusedDecoderLayerFunction.apply(x.contiguous(), y.contiguous(), cfg, key, *fused_layer_parameters(layer))

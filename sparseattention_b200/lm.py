@@ -122,6 +122,21 @@ class TransformerLM(nn.Module):
         elif isinstance(module, nn.Embedding):
             torch.nn.init.normal_(module.weight, mean=0.0, std=0.02)
 
+    def _bf16_weights(self, x, y, mask):
+        """The layers' bfloat16 weight copies, refreshed for this call, when every layer takes the fused path."""
+        layers = list(self.layers)
+        if not layers or not all(layer.fused and type(layer.self_attn) is HierarchicalAttention for layer in layers):
+            return None
+        from .fused_layer import Bf16Weights, fused_layer_supported
+        if not fused_layer_supported(layers[0], x, y, mask):
+            return None
+        cache = getattr(self, "_w16_cache", None)
+        if cache is None or not cache.matches(layers):
+            cache = Bf16Weights(layers)
+            object.__setattr__(self, "_w16_cache", cache)       # not a parameter, buffer or submodule
+        cache.refresh()
+        return cache
+
     def forward(self, trg, return_attention: bool = False, padded_logits: bool = False, hidden_only: bool = False):
         """Logits [B, N, vocab_size]; with padded_logits=True the [B, N, vocab_padded] tensor the LM head
         produces (columns >= vocab_size are padding), which `lm_loss` consumes without a copy; with
@@ -130,11 +145,16 @@ class TransformerLM(nn.Module):
         x = self.pos_encoding(x)
         y = self._span_init(x)
         causal_flag = torch.ones(1, dtype=torch.bool, device=trg.device)    # only `is not None` matters
-        for layer in self.layers:
+        w16 = None if return_attention else self._bf16_weights(x, y, causal_flag)
+        for i, layer in enumerate(self.layers):
             if return_attention:
                 x, y, _ = layer(x, y, mask=causal_flag, return_attention=True)
             else:
-                x, y = layer(x, y, mask=causal_flag)
+                layer._w16 = None if w16 is None else w16.per_layer[i]
+                try:
+                    x, y = layer(x, y, mask=causal_flag)
+                finally:
+                    layer._w16 = None            # a layer called on its own converts its weights itself
         if hidden_only:
             return x
         logits = self.fc_out(x)
