@@ -320,31 +320,40 @@ span_fwd_tc128_kernel(const SpanTc128Args a, const __grid_constant__ SpanTc128Ma
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    // one key block times one 128-byte half of the V rows
+    auto pv = [&](int bi, int hf) {
+        const int vrow = key_row(bi, (lane & 7) + 8 * ((lane >> 3) & 1));
+        const uint32_t vb = smem_u32(v_plane(hf) + (size_t)vrow * 128);
+        const int vsw = ((lane >> 4) ^ vrow) & 7;
 #pragma unroll
-    for (int hf = 0; hf < NH; ++hf) {
-        if (hf == 1 && split) {
-            if (!__syncthreads_and(mbar_wait_phase0(mbV2, a.wait_limit))) {   // the second half has landed
-                give_up();
-                return;
-            }
+        for (int dq = 0; dq < 4; ++dq) {
+            const int dp = 4 * hf + dq;
+            uint32_t vf[4];
+            ldmatrix_x4_trans(vf, vb + (((2 * dq) & 7) ^ vsw) * 16);
+            mma16816<T>(o[2 * dp], pa[bi], vf[0], vf[1]);
+            mma16816<T>(o[2 * dp + 1], pa[bi], vf[2], vf[3]);
         }
-        const unsigned char *Vp = v_plane(hf);
+    };
+    if (!split) {
+        // all of a block's columns before the next block: 2 * D / 16 independent accumulations between dependent ones
 #pragma unroll
         for (int bi = 0; bi < NB; ++bi) {
             if (bi < nblk) {
-                const int vrow = key_row(bi, (lane & 7) + 8 * ((lane >> 3) & 1));
-                const uint32_t vb = smem_u32(Vp + (size_t)vrow * 128);
-                const int vsw = ((lane >> 4) ^ vrow) & 7;
 #pragma unroll
-                for (int dq = 0; dq < 4; ++dq) {
-                    const int dp = 4 * hf + dq;
-                    uint32_t vf[4];
-                    ldmatrix_x4_trans(vf, vb + (((2 * dq) & 7) ^ vsw) * 16);
-                    mma16816<T>(o[2 * dp], pa[bi], vf[0], vf[1]);
-                    mma16816<T>(o[2 * dp + 1], pa[bi], vf[2], vf[3]);
-                }
+                for (int hf = 0; hf < NH; ++hf) pv(bi, hf);
             }
         }
+    } else {
+#pragma unroll
+        for (int bi = 0; bi < NB; ++bi)
+            if (bi < nblk) pv(bi, 0);
+        if (!__syncthreads_and(mbar_wait_phase0(mbV2, a.wait_limit))) {       // the second half has landed
+            give_up();
+            return;
+        }
+#pragma unroll
+        for (int bi = 0; bi < NB; ++bi)
+            if (bi < nblk) pv(bi, 1);
     }
 
     // ---------------------------------------------------------------- epilogue: park the rows in K's first rows, store 16 B per lane

@@ -279,7 +279,7 @@ def test_tensor_core_kernel_refuses_what_it_cannot_take(hsa):
     qb = torch.randn(1, 128, 1, 64, device="cuda", dtype=torch.bfloat16)
     kvb = torch.randn(1, 255, 1, 64, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(HsaError):
-        F.span_attention_forward(qb, kvb, kvb, 17, True, algo=4)                 # radius beyond the 128-leaf kernel
+        F.span_attention_forward(qb, kvb, kvb, 33, True, algo=4)                 # radius beyond the 128-leaf kernel
     with pytest.raises(HsaError):
         F.span_attention_forward(qb, kvb, kvb, 4, False, algo=4)                 # not causal
 
