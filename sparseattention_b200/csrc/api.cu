@@ -68,6 +68,11 @@ int hsa_span_attn_bwd_tc(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, const
                          hsa_view dK, hsa_view dV, void *workspace, int B, int N, int H, int D, int radius, int causal,
                          int dtype, cudaStream_t st);
 
+bool hsa_span_attn_fwd_f32_supported(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, int B, int N, int H, int D, int radius,
+                                     int causal, int dtype);
+int hsa_span_attn_fwd_f32(hsa_view Q, hsa_view K, hsa_view V, hsa_view Out, float *LSE, int B, int N, int H, int D, int radius,
+                          int causal, int dtype, cudaStream_t st);
+
 extern "C" int hsa_version(void) { return 200; }   // 0.2.0
 
 extern "C" int hsa_copy_rows_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t row_bytes,
@@ -102,6 +107,9 @@ extern "C" int hsa_span_attn_fwd(hsa_view Q, hsa_view K, hsa_view V, hsa_view Ou
         return hsa_span_attn_fwd_tc128(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, st);
     if (algo == 2 || (algo == 0 && hsa_span_attn_fwd_tc_supported(Q, K, V, Out, B, N, H, D, radius, causal, dtype)))
         return hsa_span_attn_fwd_tc(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, (cudaStream_t)stream);
+    // float32: the tile-staged kernel where it applies (head dim 64 / 128), the portable gather otherwise
+    if (algo == 0 && hsa_span_attn_fwd_f32_supported(Q, K, V, Out, B, N, H, D, radius, causal, dtype))
+        return hsa_span_attn_fwd_f32(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, st);
     return hsa_span_attn_fwd_generic(Q, K, V, Out, LSE, B, N, H, D, radius, causal, dtype, (cudaStream_t)stream);
 }
 

@@ -226,6 +226,16 @@ TC_CASES = [(1, 64, 1, 64, 0), (2, 64, 3, 64, 5), (1, 128, 2, 128, 16), (2, 256,
             (1, 16384, 1, 64, 16), (1, 65536, 1, 64, 1)]
 
 
+@pytest.mark.parametrize("case", [(2, 64, 3, 64, 0), (1, 64, 1, 64, 16), (2, 512, 4, 64, 16), (1, 128, 2, 64, 1), (1, 1024, 5, 64, 40),
+                                  (1, 32, 2, 128, 3), (2, 256, 3, 128, 16), (1, 4096, 2, 128, 16), (1, 8192, 1, 64, 7),
+                                  (1, 2048, 2, 128, 33)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_span_attention_fp32_staged_forward(hsa, case, causal):
+    """float32 with head dim 64 / 128: the automatic choice stages a tile's rows in shared memory (forward); same bound
+    as the portable kernel, which stays the backward and the fallback."""
+    run_span_case(hsa, *case, causal, torch.float32, algo=0)
+
+
 @pytest.mark.parametrize("case", TC_CASES)
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
