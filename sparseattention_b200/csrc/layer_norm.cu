@@ -101,8 +101,12 @@ layer_norm_bwd_kernel(const T *__restrict__ x, const TY *__restrict__ dy, const 
     }
     for (int64_t r = (int64_t)blockIdx.x * kLnWarps + warp; r < rows; r += warps) {
         const float mu = mean[r], rs = rstd[r];
-        float4 xh[NV], gy[NV];
+        float4 xh[NV], gy[NV], old[NV];
         float s1 = 0.f, s2 = 0.f;
+        // every load of the row is issued before the first reduction waits: the residual's gradient too
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            old[i] = add != nullptr ? ln_load4<T>(add + r * d + 4 * (lane + 32 * i)) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const float4 xv = ln_load4<T>(x + r * d + 4 * (lane + 32 * i));
@@ -120,10 +124,7 @@ layer_norm_bwd_kernel(const T *__restrict__ x, const TY *__restrict__ dy, const 
             float4 o;
             o.x = rs * (gy[i].x - m1 - xh[i].x * m2); o.y = rs * (gy[i].y - m1 - xh[i].y * m2);
             o.z = rs * (gy[i].z - m1 - xh[i].z * m2); o.w = rs * (gy[i].w - m1 - xh[i].w * m2);
-            if (add != nullptr) {                                 // the gradient arriving through the residual connection
-                const float4 old = ln_load4<T>(add + r * d + 4 * (lane + 32 * i));
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-            }
+            o.x += old[i].x; o.y += old[i].y; o.z += old[i].z; o.w += old[i].w;   // the gradient arriving through the residual connection
             ln_store4<T>(dx + r * d + 4 * (lane + 32 * i), o);
         }
     }
