@@ -118,31 +118,31 @@ column_sums_kernel(const __nv_bfloat16 *__restrict__ x, int64_t row_stride, int6
     });
 }
 
-// out[c] = sum over blocks of partial[block][c].  A thread block owns 32 columns; its 8 warps sum interleaved slices of
-// the block list (block w, w + 8, ..., four loads in flight each) and the 8 slice sums are added in slice order: the order
-// of additions is fixed, so the result is reproducible.
-__global__ void __launch_bounds__(256)
+// out[c] = sum over blocks of partial[block][c].  A thread block owns 32 columns; its 32 warps sum interleaved slices of
+// the block list (block w, w + 32, ..., four loads in flight each) and the 32 slice sums are added in slice order: the
+// order of additions is fixed, so the result is reproducible.
+__global__ void __launch_bounds__(1024)
 column_sums_reduce_kernel(const float *__restrict__ partial, int blocks, int cols, float *__restrict__ out) {
-    __shared__ float slice[8][32];
+    __shared__ float slice[32][33];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + lane;
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
     if (c < cols) {
         int b = w;
-        for (; b + 24 < blocks; b += 32) {
+        for (; b + 96 < blocks; b += 128) {
             s0 += partial[(int64_t)b * cols + c];
-            s1 += partial[(int64_t)(b + 8) * cols + c];
-            s2 += partial[(int64_t)(b + 16) * cols + c];
-            s3 += partial[(int64_t)(b + 24) * cols + c];
+            s1 += partial[(int64_t)(b + 32) * cols + c];
+            s2 += partial[(int64_t)(b + 64) * cols + c];
+            s3 += partial[(int64_t)(b + 96) * cols + c];
         }
-        for (; b < blocks; b += 8) s0 += partial[(int64_t)b * cols + c];
+        for (; b < blocks; b += 32) s0 += partial[(int64_t)b * cols + c];
     }
     slice[w][lane] = (s0 + s1) + (s2 + s3);
     __syncthreads();
     if (w == 0 && c < cols) {
         float t = slice[0][lane];
 #pragma unroll
-        for (int i = 1; i < 8; ++i) t += slice[i][lane];
+        for (int i = 1; i < 32; ++i) t += slice[i][lane];
         out[c] = t;
     }
 }
@@ -262,7 +262,7 @@ extern "C" int hsa_column_sums(const void *x, long long row_stride, long long ro
     dim3 grid((unsigned)((cols + 511) / 512), (unsigned)blocks);
     column_sums_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)x, row_stride, rows, cols, partial);
     if (int rc = launch_status("hsa_column_sums")) return rc;
-    column_sums_reduce_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, (cudaStream_t)stream>>>(partial, blocks, cols, out);
+    column_sums_reduce_kernel<<<(unsigned)((cols + 31) / 32), 1024, 0, (cudaStream_t)stream>>>(partial, blocks, cols, out);
     return launch_status("hsa_column_sums(reduce)");
 }
 
@@ -281,7 +281,7 @@ extern "C" int hsa_dropout_cast_colsum(const float *in, long long in_row_stride,
     dropout_cast_colsum_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(in, in_row_stride, (__nv_bfloat16 *)out, out_row_stride, rows, cols,
                                                                       rng_state, site0, site1, threshold, scale, partial);
     if (int rc = launch_status("hsa_dropout_cast_colsum")) return rc;
-    column_sums_reduce_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, (cudaStream_t)stream>>>(partial, blocks, cols, col_sums);
+    column_sums_reduce_kernel<<<(unsigned)((cols + 31) / 32), 1024, 0, (cudaStream_t)stream>>>(partial, blocks, cols, col_sums);
     return launch_status("hsa_dropout_cast_colsum(reduce)");
 }
 
@@ -298,7 +298,7 @@ extern "C" int hsa_cross_entropy_bwd_inplace(void *logits, long long row_stride,
     ce_bwd_colsum_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16 *)logits, row_stride, targets, lse, grad_scale, rows, V,
                                                                 Vp, smoothing, ignore_index, partial);
     if (int rc = launch_status("hsa_cross_entropy_bwd_inplace")) return rc;
-    column_sums_reduce_kernel<<<(unsigned)((Vp + 31) / 32), 256, 0, (cudaStream_t)stream>>>(partial, blocks, Vp, col_sums);
+    column_sums_reduce_kernel<<<(unsigned)((Vp + 31) / 32), 1024, 0, (cudaStream_t)stream>>>(partial, blocks, Vp, col_sums);
     return launch_status("hsa_cross_entropy_bwd_inplace(reduce)");
 }
 

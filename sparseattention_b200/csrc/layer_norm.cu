@@ -147,24 +147,30 @@ layer_norm_bwd_kernel(const T *__restrict__ x, const TY *__restrict__ dy, const 
     }
 }
 
-// dgamma[c] = sum over CTAs of partial[cta][0][c], dbeta likewise.  A block owns 32 columns; its 8 warps sum
-// interleaved slices of the CTA list (CTA w, w+8, ...) and the 8 slice sums are added in slice order: the
+// dgamma[c] = sum over CTAs of partial[cta][0][c], dbeta likewise.  A block owns 32 columns; its 32 warps sum
+// interleaved slices of the CTA list (CTA w, w+32, ...) and the 32 slice sums are added in slice order: the
 // order of additions is fixed, so the result is reproducible.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 layer_norm_bwd_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dgamma,
                              float *__restrict__ dbeta, int nctas, int d) {
-    __shared__ float slice[8][32];
+    __shared__ float slice[32][33];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + lane;                      // column in [0, 2d): dgamma then dbeta
-    float s = 0.f;
-    if (c < 2 * d)
-        for (int k = w; k < nctas; k += 8) s += partial[(int64_t)k * 2 * d + c];
-    slice[w][lane] = s;
+    float s0 = 0.f, s1 = 0.f;
+    if (c < 2 * d) {
+        int k = w;
+        for (; k + 32 < nctas; k += 64) {
+            s0 += partial[(int64_t)k * 2 * d + c];
+            s1 += partial[(int64_t)(k + 32) * 2 * d + c];
+        }
+        for (; k < nctas; k += 32) s0 += partial[(int64_t)k * 2 * d + c];
+    }
+    slice[w][lane] = s0 + s1;
     __syncthreads();
     if (w == 0 && c < 2 * d) {
         float t = slice[0][lane];
 #pragma unroll
-        for (int i = 1; i < 8; ++i) t += slice[i][lane];
+        for (int i = 1; i < 32; ++i) t += slice[i][lane];
         (c < d ? dgamma : dbeta)[c % d] = t;
     }
 }
@@ -230,7 +236,7 @@ extern "C" int hsa_layer_norm_bwd(const void *x, const void *dy, const float *ga
             layer_norm_bwd_kernel<T, NV><<<ctas, kLnWarps * 32, 0, (cudaStream_t)stream>>>(
                 (const T *)x, (const T *)dy, gamma, mean, rstd, (T *)dx, partial, rows);
             if ((rc = launch_status("hsa_layer_norm_bwd"))) return;
-            layer_norm_bwd_reduce_kernel<<<(2 * d + 31) / 32, 256, 0, (cudaStream_t)stream>>>(partial, dgamma, dbeta, ctas, d);
+            layer_norm_bwd_reduce_kernel<<<(2 * d + 31) / 32, 1024, 0, (cudaStream_t)stream>>>(partial, dgamma, dbeta, ctas, d);
             rc = launch_status("hsa_layer_norm_bwd(reduce)");
         });
         if (!ok) return fail(HSA_ERR_ARG, "hsa_layer_norm_bwd: width %d not supported (128, 256, 384, 512, 768)", d);
@@ -270,7 +276,7 @@ extern "C" int hsa_layer_norm_bwd_mixed(const float *x, const void *dy_bf16, con
         layer_norm_bwd_kernel<float, NV, __nv_bfloat16><<<ctas, kLnWarps * 32, 0, (cudaStream_t)stream>>>(
             x, (const __nv_bfloat16 *)dy_bf16, gamma, mean, rstd, dx, partial, rows, add);
         if ((rc = launch_status("hsa_layer_norm_bwd_mixed"))) return;
-        layer_norm_bwd_reduce_kernel<<<(2 * d + 31) / 32, 256, 0, (cudaStream_t)stream>>>(partial, dgamma, dbeta, ctas, d);
+        layer_norm_bwd_reduce_kernel<<<(2 * d + 31) / 32, 1024, 0, (cudaStream_t)stream>>>(partial, dgamma, dbeta, ctas, d);
         rc = launch_status("hsa_layer_norm_bwd_mixed(reduce)");
     });
     if (!ok) return fail(HSA_ERR_ARG, "hsa_layer_norm_bwd_mixed: width %d not supported (128, 256, 384, 512, 768)", d);
