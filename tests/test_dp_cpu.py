@@ -68,6 +68,60 @@ def test_bucketed_grad_average_gloo_world2():
         assert torch.allclose(got_g, want_g, atol=1e-6), r
 
 
+class _Tied(nn.Module):
+    """A parameter used twice in one forward (as the LM's embedding / head matrix is)."""
+
+    def __init__(self):
+        super().__init__()
+        self.emb = nn.Embedding(12, 8)
+        self.mid = nn.Linear(8, 8)
+
+    def forward(self, ids):
+        return self.mid(self.emb(ids)) @ self.emb.weight.t()
+
+
+def _tied_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    from sparseattention_b200.dp import BucketedGradAverager
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.manual_seed(1)
+    model = _Tied()
+    avg = BucketedGradAverager(model.parameters(), bucket_bytes=128)
+    gen = torch.Generator().manual_seed(7 + rank)
+    for step in range(2):
+        ids = torch.randint(0, 12, (5,), generator=gen)
+        avg.zero_grad()
+        model(ids).pow(2).mean().backward()
+        avg.finish()
+    out[rank] = torch.cat([p.grad.flatten() for p in model.parameters()])
+    dist.destroy_process_group()
+
+
+def test_bucketed_grad_average_with_a_tied_parameter():
+    world = 2
+    port = 31500 + (os.getpid() % 2000)
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_tied_worker, args=(world, port, out), nprocs=world, join=True)
+    torch.manual_seed(1)
+    model = _Tied()
+    gens = [torch.Generator().manual_seed(7 + r) for r in range(world)]
+    want = None
+    for step in range(2):
+        want = None
+        for r in range(world):
+            ids = torch.randint(0, 12, (5,), generator=gens[r])
+            model.zero_grad()
+            model(ids).pow(2).mean().backward()
+            g = torch.cat([p.grad.flatten() for p in model.parameters()])
+            want = g if want is None else want + g
+        want = want / world
+    for r in range(world):
+        assert torch.allclose(out[r], want, atol=1e-6), r
+
+
 def test_zipf_tokens_shape_and_skew():
     sys.path.insert(0, ROOT)
     from sparseattention_b200.lm import zipf_tokens

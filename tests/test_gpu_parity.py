@@ -932,6 +932,30 @@ def test_language_model_bf16_autocast_training_step(hsa):
         assert rel_err(got[name].grad.float().cpu(), want[name].grad) < 2e-2, name
 
 
+def test_language_model_weight_copies_follow_the_weights(hsa):
+    """The model keeps bfloat16 copies of its layers' weights for the fused layers and refreshes them at every forward: after
+    a weight changes in place (an optimizer step) the fused path has to see the new value, like the module-by-module path."""
+    from sparseattention_b200.lm import TransformerLM
+    torch.manual_seed(5)
+    model = TransformerLM(1000, 256, 4, 512, 2, dropout=0.0, window_size=8).cuda().eval()
+    tokens = torch.randint(0, 1000, (2, 256), device="cuda")
+
+    def run(fused):
+        for layer in model.layers:
+            layer.fused = fused
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            return model(tokens, hidden_only=True).float()
+
+    before = run(True)
+    assert getattr(model, "_w16_cache", None) is not None           # the fused path ran and built its copies
+    with torch.no_grad():
+        model.layers[0].feed_forward.fc1.weight.mul_(1.5)
+        model.layers[1].self_attn.Wv_x.weight.add_(0.05)
+    after_fused, after_eager = run(True), run(False)
+    assert rel_err(after_fused.cpu(), after_eager.cpu()) < 2e-2
+    assert rel_err(after_fused.cpu(), before.cpu()) > 5e-2          # the change is large enough to tell stale copies apart
+
+
 # ------------------------------------------------------------------------------------- incremental decoding
 @pytest.mark.parametrize("case", [(2, 16, 3, 24, 2), (1, 64, 2, 32, 5), (3, 256, 4, 64, 16), (1, 1024, 12, 64, 16)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
