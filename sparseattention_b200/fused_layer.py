@@ -345,14 +345,14 @@ class FusedDecoderLayerFunction(torch.autograd.Function):
                         spec(S_CHILD).apply(dkv, dkv, d, d, 2 * d, M, po)
                     # the children are the outputs of the level below: their gradient gets this level's share
                     gemm(dkv, Wkv_y, b_t=True, out=dRf[:, po:po + pp], accumulate=True, copy_bf16=dRb[:, po:po + pp])
-            # child projections: leaves from x, every higher level from the refreshed rows below it, one product each
-            dWkv_y = gemm(dKVc0, xb, a_t=True, b_t=True, out_dtype=f32)
+            # [Wq_y; Wk_y; Wv_y] in one buffer: the parents' own projections give all three, the child projections (leaves
+            # from x, every higher level from the refreshed rows below it, one product each) add to the K and V parts
+            dWqkv_y = gemm(dQKVp, yn, a_t=True, b_t=True, out_dtype=f32)
+            gemm(dKVc0, xb, a_t=True, b_t=True, out=dWqkv_y[d:], accumulate=True)
             if M > 1:
-                gemm(dKVc[:, :M - 1], Rb[:, :M - 1], a_t=True, b_t=True, out=dWkv_y, accumulate=True)
+                gemm(dKVc[:, :M - 1], Rb[:, :M - 1], a_t=True, b_t=True, out=dWqkv_y[d:], accumulate=True)
             dx = new(B, N, d, dtype=f32)
             gemm(dKVc0, Wkv_y, b_t=True, out=dx, residual=dx_a)
-            dWqkv_y = gemm(dQKVp, yn, a_t=True, b_t=True, out_dtype=f32)
-            dWqkv_y[d:] += dWkv_y
             dyn = gemm(dQKVp, Wqkv_y, b_t=True)
             dy, dgy, dby = _ln_bwd(y, dyn, gy, mean_y, rstd_y, dyn_total)
 
