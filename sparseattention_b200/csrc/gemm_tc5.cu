@@ -41,6 +41,14 @@ constexpr int kBM = 128, kBK = 64;
 constexpr int kEpiWarps = 8;                      // two warps per tensor-memory lane quarter, half the columns each
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 
+// Stage geometry shared by the kernel and its launcher.
+__host__ __device__ constexpr int gemm_bk(bool a_mn, bool b_mn) { return (a_mn && b_mn) ? 128 : kBK; }
+__host__ __device__ constexpr int gemm_staging_bytes(bool a_mn, bool b_mn) { return (a_mn && b_mn) ? 0 : 65536; }
+__host__ __device__ constexpr int gemm_stages(int stage_bytes, int staging_bytes) {
+    int n = (227 * 1024 - 2304 - staging_bytes) / stage_bytes;      // 2304: bias values, barriers, alignment slack
+    return n > 6 ? 6 : n;
+}
+
 struct GemmArgs {
     void *c;                      // [batches, rows, N] (OutT), element strides below
     int64_t c_bs, c_rs;
@@ -79,9 +87,15 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
     using namespace tc5;
     constexpr int B_ROWS = TWO ? BN / 2 : BN;          // rows of the B tile this CTA stages
     constexpr int MT = TWO ? 2 * kBM : kBM;            // rows of a tile
-    constexpr int A_BYTES = kBM * 128, B_BYTES = B_ROWS * 128;
+    // K extent of a stage.  With both operands stored transposed a stage is four boxes of [BK rows][64 elements]; the copy
+    // engine takes about as long for an 8 KB box as for a 16 KB one (measured: ~230 cycles either way), so those products
+    // use 128-row boxes: the same four boxes then carry twice the K.  They write their (float32) results with plain stores
+    // and have no output staging blocks; their room goes to the stages.
+    constexpr int BK = gemm_bk(A_MN, B_MN);
+    constexpr int A_BYTES = kBM * 2 * BK, B_BYTES = B_ROWS * 2 * BK;
     constexpr int STAGE = A_BYTES + B_BYTES;
-    constexpr int STAGES = STAGE == 49152 ? 3 : (STAGE == 32768 ? 5 : 6);
+    constexpr int STG_BYTES = gemm_staging_bytes(A_MN, B_MN);
+    constexpr int STAGES = gemm_stages(STAGE, STG_BYTES);
     constexpr uint32_t IDESC = instr_desc(MT, BN, true, A_MN, B_MN);
     const uint32_t rank = TWO ? cluster_ctarank() : 0;  // 0 = the CTA that issues the MMAs
     const int unit = TWO ? blockIdx.x / 2 : blockIdx.x, nunits = TWO ? gridDim.x / 2 : gridDim.x;
@@ -89,8 +103,8 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     unsigned char *staging = smem + (size_t)STAGES * STAGE;           // 2 x 2 x 16 KB: two blocks of output rows per column half
-    float *bias_s = reinterpret_cast<float *>(staging + 65536);        // the tile's bias values, 128 per column half
-    unsigned long long *bars = reinterpret_cast<unsigned long long *>(staging + 65536 + 1024);
+    float *bias_s = reinterpret_cast<float *>(staging + STG_BYTES);    // the tile's bias values, 128 per column half
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(staging + STG_BYTES + 1024);
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -158,18 +172,18 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                     const uint32_t sa = smem_addr(smem + (size_t)s * STAGE), sb = sa + A_BYTES;
                     // K position of this step: a plain K offset, or (batch entry, row offset) when K runs over rows of a
                     // batch-strided tensor
-                    const int kbatch = kb / a.kb_per_batch, krow = (kb % a.kb_per_batch) * kBK;
+                    const int kbatch = kb / a.kb_per_batch, krow = (kb % a.kb_per_batch) * BK;
                     if constexpr (!A_MN) {
-                        load(sa, &map_a, kb * kBK, m0, b, fb);
+                        load(sa, &map_a, kb * BK, m0, b, fb);
                     } else {
 #pragma unroll
-                        for (int p = 0; p < kBM / 64; ++p) load(sa + p * (kBK * 128), &map_a, m0 + p * 64, krow, kbatch, fb);
+                        for (int p = 0; p < kBM / 64; ++p) load(sa + p * (BK * 128), &map_a, m0 + p * 64, krow, kbatch, fb);
                     }
                     if constexpr (!B_MN) {
-                        load(sb, &map_b, kb * kBK, n0, 0, fb);
+                        load(sb, &map_b, kb * BK, n0, 0, fb);
                     } else {
 #pragma unroll
-                        for (int p = 0; p < B_ROWS / 64; ++p) load(sb + p * (kBK * 128), &map_b, n0 + p * 64, krow, kbatch, fb);
+                        for (int p = 0; p < B_ROWS / 64; ++p) load(sb + p * (BK * 128), &map_b, n0 + p * 64, krow, kbatch, fb);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -197,9 +211,9 @@ gemm_tc5_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_a, con
                     fence_after_sync();
                     const uint32_t sa = smem_addr(smem + (size_t)s * STAGE), sb = sa + A_BYTES;
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {
-                        const uint64_t da = A_MN ? smem_desc(sa + k * 2048, kBK * 128, 1024) : smem_desc(sa + k * 32, 16, 1024);
-                        const uint64_t db = B_MN ? smem_desc(sb + k * 2048, kBK * 128, 1024) : smem_desc(sb + k * 32, 16, 1024);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t da = A_MN ? smem_desc(sa + k * 2048, BK * 128, 1024) : smem_desc(sa + k * 32, 16, 1024);
+                        const uint64_t db = B_MN ? smem_desc(sb + k * 2048, BK * 128, 1024) : smem_desc(sb + k * 32, 16, 1024);
                         if constexpr (TWO) mma_f16_pair(d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
                         else mma_f16(d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
@@ -777,12 +791,13 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
         // A stored [batches, K, rows]: C[rows, N] = sum over batch entries and k; B must be transposed as well,
         // stored [batches, K, N], so both are cut along the same (batch entry, row) steps
         HSA_CHECK_ARG(b_layout == 1, "hsa_gemm: a transposed A needs a transposed B ([K, N])");
-        g.kb_per_batch = (K + kBK - 1) / kBK;
+        constexpr int bk = gemm_bk(true, true);
+        g.kb_per_batch = (K + bk - 1) / bk;
         g.k_blocks = g.kb_per_batch * batches;
         out_batches = 1;
         g.batches = 1;
-        ok = make_map3(&ma, A.ptr, rows, K, batches, A.row_stride, A.batch_stride, kBK) &&
-             make_map3(&mb, Bm.ptr, N, K, batches, Bm.row_stride, Bm.batch_stride, kBK);
+        ok = make_map3(&ma, A.ptr, rows, K, batches, A.row_stride, A.batch_stride, bk) &&
+             make_map3(&mb, Bm.ptr, N, K, batches, Bm.row_stride, Bm.batch_stride, bk);
     }
     if (!ok)
         return fail(HSA_ERR_ARG,
@@ -805,7 +820,7 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
     // the output's tensor map (rows leave by bulk copies), unless the epilogue has to read C back or writes partial slabs
     CUtensorMap mc = ma;
     g.tma_store = 0;
-    if (g.partial == nullptr && !accumulate && !(epilogue && epilogue->ce_partial && epilogue->ce_skip_store) && make_map_out(&mc, C.ptr, N, rows, out_batches, C.row_stride, C.batch_stride, esz))
+    if (a_layout == 0 && g.partial == nullptr && !accumulate && !(epilogue && epilogue->ce_partial && epilogue->ce_skip_store) && make_map_out(&mc, C.ptr, N, rows, out_batches, C.row_stride, C.batch_stride, esz))
         g.tma_store = 1;
     const long long total = (long long)g.m_tiles * g.n_tiles * g.batches * g.splits;
     if (total > 0x7fffffffLL) return fail(HSA_ERR_ARG, "hsa_gemm: too many tiles");
@@ -814,9 +829,11 @@ extern "C" int hsa_gemm_ex(hsa_view A, hsa_view Bm, hsa_view C, const float *bia
     cudaStream_t st = (cudaStream_t)stream;
 
     auto launch = [&](auto kernel, int bn) -> int {
-        const int stage = kBM * 128 + (sh.two ? bn / 2 : bn) * 128;
-        const int stages = stage == 49152 ? 3 : (stage == 32768 ? 5 : 6);
-        const size_t smem = (size_t)stages * stage + 65536 + 1024 + (2 * stages + 4) * 8 + 16 + 1024;
+        const bool amn = a_layout != 0, bmn = b_layout != 0;
+        const int stage = (kBM + (sh.two ? bn / 2 : bn)) * 2 * gemm_bk(amn, bmn);
+        const int stg = gemm_staging_bytes(amn, bmn);
+        const int stages = gemm_stages(stage, stg);
+        const size_t smem = (size_t)stages * stage + stg + 1024 + (2 * stages + 4) * 8 + 16 + 1024;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "hsa_gemm: shared memory %zu: %s", smem, cudaGetErrorString(e));
         cudaLaunchConfig_t cfg{};
