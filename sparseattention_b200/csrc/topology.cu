@@ -110,16 +110,16 @@ __global__ void pyramid_bwd_kernel(const T *__restrict__ gy, int64_t gy_bs, int6
     float acc[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
-    // find offsets top-down: recompute offsets by walking (cheap: nlevels <= 31)
-    int64_t off[32];
+    // offset of level l = sum of the sizes of the levels below it; walked top-down from the total (no per-thread table)
     int64_t o = 0;
-    for (int l = 1; l <= nlevels; ++l) { off[l] = o; o += (N >> l); }
+    for (int l = 1; l <= nlevels; ++l) o += (N >> l);
     bool have = false;
     for (int l = nlevels; l >= 1; --l) {
+        o -= (N >> l);
         const int64_t i = n >> l;
         if (i < (int64_t)(N >> l)) {
             float v[VEC];
-            load_vec<T, VEC>(g + (off[l] + i) * gy_rs, v);
+            load_vec<T, VEC>(g + (o + i) * gy_rs, v);
 #pragma unroll
             for (int e = 0; e < VEC; ++e)
                 acc[e] = have ? Traits<T>::to_f(Traits<T>::from_f(v[e] + Traits<T>::to_f(Traits<T>::from_f(0.5f * acc[e]))))
