@@ -58,11 +58,16 @@ class BucketedGradAverager:
             b = self.buckets[bi]
             b["pending"] -= 1
             if b["pending"] == 0 and self.bucketed:
-                # the bucket's gradients are complete: one multi-tensor copy into the flat buffer, then its all-reduce
-                torch._foreach_copy_(b["views"], [p.grad for p in b["params"]])
+                # the bucket's gradients are complete: one multi-tensor copy into the flat buffer, then its all-reduce.
+                # A bucket of one parameter (the tied embedding / head matrix, whose gradient arrives last) is reduced
+                # where autograd left it: no copy stands between the end of the backward and the collective.
+                single = len(b["params"]) == 1 and b["params"][0].grad.is_contiguous()
+                b["reduced"] = b["params"][0].grad if single else b["flat"]
+                if not single:
+                    torch._foreach_copy_(b["views"], [p.grad for p in b["params"]])
                 if self.world > 1:
                     op = dist.ReduceOp.AVG if self._avg_op else dist.ReduceOp.SUM
-                    self._handles.append((dist.all_reduce(b["flat"], op=op, group=self.group, async_op=True), bi))
+                    self._handles.append((dist.all_reduce(b["reduced"], op=op, group=self.group, async_op=True), bi))
         return hook
 
     def zero_grad(self):
@@ -79,12 +84,12 @@ class BucketedGradAverager:
         for h, bi in self._handles:
             h.wait()
             if not self._avg_op and self.world > 1:
-                self.buckets[bi]["flat"].div_(self.world)
+                self.buckets[bi]["reduced"].div_(self.world)
         self._handles.clear()
         for b in self.buckets:
             if b["pending"] != 0 and self.world > 1:
                 raise RuntimeError("a parameter received no gradient this step; its bucket was never reduced")
-            if self.bucketed and b["pending"] == 0:
+            if self.bucketed and b["pending"] == 0 and b.get("reduced") is b["flat"]:
                 for p, v in zip(b["params"], b["views"]):
                     p.grad = v
 
